@@ -121,3 +121,5 @@ def _ensure_builtin() -> None:
     _s.register()
     from ..models import damadra as _d
     _d.register()
+    from ..models import molitar as _m
+    _m.register()

@@ -23,8 +23,11 @@
 // r1 log2(1 + r2 (i - j)); and a factor on the output.  Two more serve attention with a learned bias by distance and
 // value heads of their own size: a float table bias[head][min(i - j, rows - 1)] that is added to the scaled score
 // (the last column stands for every greater distance), and dv != d (a page is then [K: KH x page x d | V: KH x page x
-// dv]; the tiles are as wide as the larger of the two, the narrower zero-filled).  Without them the kernels are
-// what they were.
+// dv]; the tiles are as wide as the larger of the two, the narrower zero-filled).  Four more: scores squashed to
+// cap * tanh(score / cap); a sink per query head that joins the softmax's denominator as exp(sink[h]) and brings no
+// value (added once: by the CTA where the keys are not split, else by the merge); values that are the first dv columns
+// of the key rows (a page then holds keys only); and a gate, out *= sigmoid(gate[t][h * dv + i]), on float rows with a
+// stride of their own.  Without them the kernels are what they were.
 //
 // Head sizes: the template is instantiated for 32, 64, 128 and 256; a head size that is a
 // multiple of 8 below the next instance is zero-padded in shared memory.
@@ -57,7 +60,14 @@ struct FaArgs {
     int dv;                            // the value heads' size (= d unless the layer says otherwise)
     const float* bias;                 // [QH, bias_rows] added to the scaled scores by distance (null: none)
     int bias_rows;
+    float cap_log2, scale_over_cap;    // soft cap: score <- cap tanh(score / cap), here cap * log2 e and scale / cap (0: none)
+    const float* sink;                 // [QH] one more term exp(sink[h]) in the denominator (null: none)
+    int v_in_k;                        // != 0: the values are the first dv columns of the key rows; pages hold keys only
+    const float* gate;                 // out *= sigmoid(gate[t * gate_stride + h * dv + i]) (null: none)
+    long long gate_stride;
 };
+
+__device__ __forceinline__ float fa_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // ---------------------------------------------------------------- small PTX wrappers
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
@@ -105,10 +115,11 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
     static_assert(FA_THREADS % CPR == 0 && FA_BN % RPI == 0, "tile shape");
     const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
     const bool kcol_ok = c * 8 < a.d, vcol_ok = c * 8 < a.dv;
-    const size_t head_stride = (size_t)a.page_size * a.d, vhead_stride = (size_t)a.page_size * a.dv;
-    const size_t page_stride = (size_t)a.KH * (head_stride + vhead_stride);
+    const size_t head_stride = (size_t)a.page_size * a.d, vhead_stride = a.v_in_k ? head_stride : (size_t)a.page_size * a.dv;
+    const size_t page_stride = a.v_in_k ? (size_t)a.KH * head_stride : (size_t)a.KH * (head_stride + vhead_stride);
+    const int v_row = a.v_in_k ? a.d : a.dv;
     const bf16* kbase = a.cache + (size_t)kh * head_stride + c * 8;
-    const bf16* vbase = a.cache + (size_t)a.KH * head_stride + (size_t)kh * vhead_stride + c * 8;
+    const bf16* vbase = a.cache + (a.v_in_k ? 0 : (size_t)a.KH * head_stride) + (size_t)kh * vhead_stride + c * 8;
     unsigned char* dst0 = stage + r0 * FaSmem<D>::STRIDE + c * 16;
 #pragma unroll
     for (int i = 0; i < FA_BN / RPI; ++i) {
@@ -123,7 +134,7 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
             const int page = pi < a.max_pages ? bt[pi] : -1;
             if (page >= 0) {
                 if (kcol_ok) { ksrc = kbase + (size_t)page * page_stride + (size_t)off * a.d; kbytes = 16; }
-                if (vcol_ok) { vsrc = vbase + (size_t)page * page_stride + (size_t)off * a.dv; vbytes = 16; }
+                if (vcol_ok) { vsrc = vbase + (size_t)page * page_stride + (size_t)off * v_row; vbytes = 16; }
             }
         }
         unsigned char* dst = dst0 + i * RPI * FaSmem<D>::STRIDE;
@@ -140,7 +151,8 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
                                         int koff, int k0_abs, int pos0, int pos1, int lo0, int lo1, float scale_log2,
                                         float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                         bool pen = false, float pa0 = 0.0f, float pb0 = 0.0f, float pa1 = 0.0f, float pb1 = 0.0f,
-                                        const float* bias0 = nullptr, const float* bias1 = nullptr, int bias_stride = 0, int bias_last = 0) {
+                                        const float* bias0 = nullptr, const float* bias1 = nullptr, int bias_stride = 0, int bias_last = 0,
+                                        float cap_log2 = 0.0f, float scale_over_cap = 0.0f) {
     constexpr int STRIDE = FaSmem<D>::STRIDE;
     const int lane = threadIdx.x & 31;
     float s[NT][4];
@@ -164,6 +176,10 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
     for (int j = 0; j < NT; ++j) {
         const int key = k0_abs + koff + j * 8 + 2 * (lane & 3);
         float v0 = s[j][0] * scale_log2, v1 = s[j][1] * scale_log2, v2 = s[j][2] * scale_log2, v3 = s[j][3] * scale_log2;
+        if (cap_log2 > 0.0f) {                                 // the soft cap, in the exponent's base-2 domain
+            v0 = cap_log2 * tanhf(s[j][0] * scale_over_cap); v1 = cap_log2 * tanhf(s[j][1] * scale_over_cap);
+            v2 = cap_log2 * tanhf(s[j][2] * scale_over_cap); v3 = cap_log2 * tanhf(s[j][3] * scale_over_cap);
+        }
         if (pen) {                                             // the distance penalty (masked places are replaced below)
             v0 = fmaf(-pa0, __log2f(fmaf(pb0, (float)(pos0 - key), 1.0f)), v0);
             v1 = fmaf(-pa0, __log2f(fmaf(pb0, (float)(pos0 - key - 1), 1.0f)), v1);
@@ -301,7 +317,7 @@ fa_prefill_kernel(const FaArgs a) {
             const unsigned char* sK = stages + buf * FaSmem<D>::STAGE;
             fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, sK + FaSmem<D>::TILE, 0, t * FA_BN,
                                   pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
-                                  bias0, bias1, 1, a.bias_rows - 1);
+                                  bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap);
         }
     }
     cp_async_wait<0>();
@@ -311,16 +327,32 @@ fa_prefill_kernel(const FaArgs a) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     }
-    const float inv0 = l[0] > 0.0f ? a.out_scale / l[0] : 0.0f, inv1 = l[1] > 0.0f ? a.out_scale / l[1] : 0.0f;
+    float f0 = 1.0f, f1 = 1.0f;                                // what the sink's entry into the denominator does to the sums
+    if (a.sink) {
+        constexpr float LOG2E = 1.4426950408889634f;
+        const float s0 = a.sink[hd0] * LOG2E, s1 = a.sink[hd1] * LOG2E;
+        const float mf0 = fmaxf(m[0], s0), mf1 = fmaxf(m[1], s1);
+        f0 = exp2f(m[0] - mf0); f1 = exp2f(m[1] - mf1);
+        l[0] = l[0] * f0 + exp2f(s0 - mf0); l[1] = l[1] * f1 + exp2f(s1 - mf1);
+    }
+    const float inv0 = l[0] > 0.0f ? a.out_scale / l[0] * f0 : 0.0f, inv1 = l[1] > 0.0f ? a.out_scale / l[1] * f1 : 0.0f;
     const int tok_base = a.cu_q[e] + q0;
+    const float* g0 = (a.gate && ti0 < n_tok) ? a.gate + (size_t)(tok_base + ti0) * a.gate_stride + (size_t)hd0 * a.dv : nullptr;
+    const float* g1 = (a.gate && ti1 < n_tok) ? a.gate + (size_t)(tok_base + ti1) * a.gate_stride + (size_t)hd1 * a.dv : nullptr;
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
         const int dim = j * 8 + 2 * (lane & 3);
         if (dim >= a.dv) continue;
-        if (ti0 < n_tok)
-            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti0) * a.QH + head0 + r0 % a.Gc) * a.dv + dim) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
-        if (ti1 < n_tok)
-            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti1) * a.QH + head0 + r1 % a.Gc) * a.dv + dim) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+        if (ti0 < n_tok) {
+            float x0 = o[j][0] * inv0, x1 = o[j][1] * inv0;
+            if (g0) { x0 *= fa_sigmoid(g0[dim]); x1 *= fa_sigmoid(g0[dim + 1]); }
+            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti0) * a.QH + hd0) * a.dv + dim) = pack_bf16(x0, x1);
+        }
+        if (ti1 < n_tok) {
+            float x2 = o[j][2] * inv1, x3 = o[j][3] * inv1;
+            if (g1) { x2 *= fa_sigmoid(g1[dim]); x3 *= fa_sigmoid(g1[dim + 1]); }
+            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti1) * a.QH + hd1) * a.dv + dim) = pack_bf16(x2, x3);
+        }
     }
 }
 
@@ -374,7 +406,7 @@ fa_decode_kernel(const FaArgs a) {
         cp_async_commit();
         const unsigned char* sK = stages + (it % NST) * FaSmem<D>::STAGE;
         fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
-                      bias0, bias1, 1, a.bias_rows - 1);
+                      bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap);
     }
     cp_async_wait<0>();
     __syncthreads();                                           // the stages are free: reuse them for the merge
@@ -402,6 +434,10 @@ fa_decode_kernel(const FaArgs a) {
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
+        const int head = head0 + row;
+        const bool sunk = a.sink != nullptr && a.n_splits == 1;   // keys split over CTAs: the merge adds the sink, once
+        const float sk = sunk ? a.sink[head] * 1.4426950408889634f : -INFINITY;
+        if (sunk) M = fmaxf(M, sk);
         float L = 0.0f, O = 0.0f;
         if (M > -INFINITY) {
 #pragma unroll
@@ -410,10 +446,11 @@ fa_decode_kernel(const FaArgs a) {
                 L += sL[w * 16 + row] * f;
                 O += sO[(w * 16 + row) * D + dim] * f;
             }
+            if (sunk) L += exp2f(sk - M);
         }
-        const float val = L > 0.0f ? O / L * a.out_scale : 0.0f;
-        const int head = head0 + row;
+        float val = L > 0.0f ? O / L * a.out_scale : 0.0f;
         if (a.n_splits == 1) {
+            if (a.gate) val *= fa_sigmoid(a.gate[(size_t)tok * a.gate_stride + (size_t)head * a.dv + dim]);
             a.out[((size_t)tok * a.QH + head) * a.dv + dim] = __float2bfloat16_rn(val);
         } else {
             const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
@@ -424,13 +461,17 @@ fa_decode_kernel(const FaArgs a) {
 }
 
 // out[t, h, :] = sum_s w_s o_s / sum_s w_s,  w_s = 2^(lse_s - max lse), splits in ascending order
+// sink [QH] (null: none): one more weight 2^(sink log2 e - max) without a value; gate as in FaArgs.
 __global__ void fa_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
-                                int first_tok, int QH, int d, int n_splits) {
+                                int first_tok, int QH, int d, int n_splits, const float* __restrict__ sink,
+                                const float* __restrict__ gate, long long gate_stride) {
     pdl_trigger(); pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * QH + h) * n_splits;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_lse[base + s]);
+    const float sk = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+    M = fmaxf(M, sk);
     for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
         float W = 0.0f, O = 0.0f;
         if (M > -INFINITY) {
@@ -439,8 +480,11 @@ __global__ void fa_merge_kernel(const float* __restrict__ part_o, const float* _
                 W += w;
                 O += w * part_o[(base + s) * d + dim];
             }
+            if (sink) W += exp2f(sk - M);
         }
-        out[((size_t)(first_tok + t) * QH + h) * d + dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
+        float val = W > 0.0f ? O / W : 0.0f;
+        if (gate) val *= fa_sigmoid(gate[(size_t)(first_tok + t) * gate_stride + (size_t)h * d + dim]);
+        out[((size_t)(first_tok + t) * QH + h) * d + dim] = __float2bfloat16_rn(val);
     }
 }
 
@@ -479,6 +523,19 @@ static int fa_launch_decode(const FaArgs& a, cudaStream_t s) {
     return rb_launch(fa_decode_kernel<D, NST>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FA_THREADS), smem, s, a);
 }
 
+// What the soft cap, the sink, values inside the keys and the gate add to the arguments.
+struct FaMore {
+    float softcap; const float* sink; int v_in_k; const float* gate; long long gate_stride;
+};
+static int fa_more(FaArgs& a, const FaMore* x, float scale, int d) {
+    if (!x) return 0;
+    if (x->softcap < 0.0f) RB_REFUSE("attention: a soft cap of %g", (double)x->softcap);
+    if (x->v_in_k && a.dv > d) RB_REFUSE("attention: values inside the keys cannot be wider (%d) than the keys (%d)", a.dv, d);
+    if (x->softcap > 0.0f) { a.cap_log2 = x->softcap * 1.4426950408889634f; a.scale_over_cap = scale / x->softcap; }
+    a.sink = x->sink; a.v_in_k = x->v_in_k; a.gate = x->gate; a.gate_stride = x->gate_stride;
+    return 0;
+}
+
 static int fa_check(int QH, int KH, int d, int page_size, int max_pages, int dv = 0, const float* bias = nullptr, int bias_rows = 0) {
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
     if (d <= 0 || d % 8 || d > 256) RB_REFUSE("attention (tensor cores): head_dim %d is not a multiple of 8 up to 256", d);
@@ -495,7 +552,7 @@ extern "C" int rb_fa_group_chunk(int G) { return fa_group_chunk(G); }
 extern "C" int rb_fa_prefill(const void* q, const void* cache, const int* block_table, const int* cu_q, const int* kv_len,
                              void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d, int page_size,
                              int max_pages, int window, float scale, int chunk, const float* r1, const float* r2, float out_scale,
-                             int dv, const float* bias, int bias_rows, void* stream) {
+                             int dv, const float* bias, int bias_rows, const FaMore* more, void* stream) {
     if (n_entries <= 0 || n_tiles <= 0) return 0;
     if (fa_check(QH, KH, d, page_size, max_pages, dv, bias, bias_rows)) return -1;
     if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
@@ -506,6 +563,7 @@ extern "C" int rb_fa_prefill(const void* q, const void* cache, const int* block_
     a.out = (bf16*)out; a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = 1; a.scale_log2 = scale * 1.4426950408889634f;
+    if (fa_more(a, more, scale, d)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int wide = a.dv > d ? a.dv : d;                     // the tiles' width serves both sizes
     if (wide <= 32) return fa_launch_prefill<32>(a, n_tiles, s);
@@ -520,7 +578,7 @@ extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_t
                             void* out, float* part_o, float* part_lse, int first_entry, int n_entries, int first_tok,
                             int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window, float scale,
                             int chunk, const float* r1, const float* r2, float out_scale, int dv, const float* bias,
-                            int bias_rows, void* stream) {
+                            int bias_rows, const FaMore* more, void* stream) {
     if (n_entries <= 0) return 0;
     if (fa_check(QH, KH, d, page_size, max_pages, dv, bias, bias_rows)) return -1;
     if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
@@ -534,6 +592,7 @@ extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_t
     a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = n_splits; a.scale_log2 = scale * 1.4426950408889634f;
+    if (fa_more(a, more, scale, d)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     const int wide = a.dv > d ? a.dv : d;
@@ -543,5 +602,5 @@ extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_t
     else rc = fa_launch_decode<256, 2>(a, s);
     if (rc || n_splits == 1) return rc;
     return rb_launch(fa_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
-                     (bf16*)out, first_tok, QH, a.dv, n_splits);
+                     (bf16*)out, first_tok, QH, a.dv, n_splits, a.sink, a.gate, a.gate_stride);
 }

@@ -296,11 +296,13 @@ def gemm_ref(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool
 def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_row: torch.Tensor,
                         positions: torch.Tensor, out: torch.Tensor, QH: int, KH: int, d: int, page_size: int,
                         window: int, scale: float, work=(0.0, 0.0), dv: int = 0, chunk: int = 0,
-                        penalty=None, out_scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
+                        penalty=None, out_scale: float = 1.0, bias: Optional[torch.Tensor] = None,
+                        more: Optional["AttentionExtras"] = None) -> None:
     """The plain attention over the paged cache.  dv: the value heads' size where it differs from d (the cache of a
     layer is then [page][K: KH x page x d | V: KH x page x dv]); chunk: a token sees only the keys of its own chunk
     of that many positions; penalty = (r1, r2), float32 [QH] each: score -= r1 ln(1 + r2 (i - j)); out_scale
-    multiplies the output before it is rounded; bias: float32 [QH, rows], score += bias[h, min(i - j, rows - 1)]."""
+    multiplies the output before it is rounded; bias: float32 [QH, rows], score += bias[h, min(i - j, rows - 1)];
+    more: soft cap, sink, values inside the keys and output gate (AttentionExtras)."""
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous(),
           "attention: contiguous")
     _need(q.dtype == cache.dtype == out.dtype, "attention: one dtype for q, cache and out")
@@ -312,8 +314,51 @@ def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch
     _check(lib().rb_paged_attention_ref(_p(q), _p(cache), c_int(dt(q)), _p(block_table), _p(tok_row), _p(positions),
                                         _p(out), c_int(q.shape[0]), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
                                         c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(dv), c_int(chunk),
-                                        _p(r1), _p(r2), c_float(out_scale), *_bias_args(bias, QH), _stream()),
+                                        _p(r1), _p(r2), c_float(out_scale), *_bias_args(bias, QH),
+                                        *(more or _NO_EXTRAS).flat(QH, dv or d), _stream()),
            "paged_attention_ref", *work)
+
+
+class _FaMore(ctypes.Structure):
+    _fields_ = [("softcap", c_float), ("sink", c_void_p), ("v_in_k", c_int), ("gate", c_void_p), ("gate_stride", c_longlong)]
+
+
+class AttentionExtras:
+    """Options of the attention kernels beyond mask, penalty and bias: `softcap` > 0 squashes the scaled scores to
+    cap * tanh(score / cap); `sink` (float32 [QH]) joins each head's softmax denominator as exp(sink[h]) without a
+    value; `v_in_k`: the values are the first dv columns of the key rows and the pages hold keys only; `gate` (float32
+    rows [T, >= QH * dv], rows contiguous inside): the output is multiplied by sigmoid(gate[t, h * dv + i])."""
+
+    def __init__(self, softcap: float = 0.0, sink: Optional[torch.Tensor] = None, v_in_k: bool = False,
+                 gate: Optional[torch.Tensor] = None):
+        self.softcap, self.sink, self.v_in_k, self.gate = float(softcap or 0.0), sink, bool(v_in_k), gate
+
+    def check(self, QH: int, dv: int) -> None:
+        _need(self.sink is None or (self.sink.dtype == torch.float32 and self.sink.is_contiguous() and self.sink.numel() == QH),
+              "attention: the sink is one float32 number per query head")
+        _need(self.gate is None or (self.gate.dtype == torch.float32 and self.gate.dim() == 2 and self.gate.stride(1) == 1 and
+                                    self.gate.shape[1] == QH * dv), "attention: the gate is float32 [T, query heads * value size]")
+
+    def flat(self, QH: int, dv: int):
+        """The arguments as the plain kernel's entry point takes them, one by one."""
+        self.check(QH, dv)
+        return (c_float(self.softcap), _p(self.sink), c_int(int(self.v_in_k)), _p(self.gate),
+                c_longlong(self.gate.stride(0) if self.gate is not None else 0))
+
+    def struct(self, QH: int, dv: int):
+        """The arguments as the flash kernels' entry points take them: a pointer to one record."""
+        self.check(QH, dv)
+        self._rec = _FaMore(self.softcap, self.sink.data_ptr() if self.sink is not None else None, int(self.v_in_k),
+                            self.gate.data_ptr() if self.gate is not None else None,
+                            self.gate.stride(0) if self.gate is not None else 0)
+        return ctypes.byref(self._rec)
+
+
+_NO_EXTRAS = AttentionExtras()
+
+
+def _more_arg(more: Optional[AttentionExtras], QH: int, dv: int):
+    return c_void_p(0) if more is None else more.struct(QH, dv)
 
 
 def _bias_args(bias, QH: int):
@@ -345,7 +390,8 @@ def _penalty_args(penalty, QH: int):
 
 def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
               QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-              chunk: int = 0, penalty=None, out_scale: float = 1.0, dv: int = 0, bias: Optional[torch.Tensor] = None) -> None:
+              chunk: int = 0, penalty=None, out_scale: float = 1.0, dv: int = 0, bias: Optional[torch.Tensor] = None,
+              more: Optional[AttentionExtras] = None) -> None:
     """Split-K flash decoding (tensor cores) for entries that bring one token each.  chunk, penalty = (r1, r2),
     out_scale, dv and bias as in paged_attention_ref."""
     part_o = part_lse = None
@@ -356,7 +402,7 @@ def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entr
                               c_int(first_entry), c_int(n_entries), c_int(first_tok), c_int(n_splits), c_int(QH), c_int(KH),
                               c_int(d), c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale),
                               c_int(chunk), *_penalty_args(penalty, QH), c_float(out_scale), c_int(dv), *_bias_args(bias, QH),
-                              _stream()), "fa_decode", *work)
+                              _more_arg(more, QH, dv or d), _stream()), "fa_decode", *work)
     if n_splits > 1:
         global launches
         launches += 1                      # the merge kernel
@@ -513,13 +559,15 @@ def tma_pages(page_size: int) -> bool:
 
 def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
                QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-               chunk: int = 0, penalty=None, out_scale: float = 1.0, dv: int = 0, bias: Optional[torch.Tensor] = None) -> None:
+               chunk: int = 0, penalty=None, out_scale: float = 1.0, dv: int = 0, bias: Optional[torch.Tensor] = None,
+               more: Optional[AttentionExtras] = None) -> None:
     """Paged causal flash attention (tensor cores) for entries that bring several tokens.  chunk, penalty = (r1, r2),
     out_scale, dv and bias as in paged_attention_ref."""
     _check(lib().rb_fa_prefill(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), c_int(first_entry),
                                c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
                                c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(chunk),
-                               *_penalty_args(penalty, QH), c_float(out_scale), c_int(dv), *_bias_args(bias, QH), _stream()),
+                               *_penalty_args(penalty, QH), c_float(out_scale), c_int(dv), *_bias_args(bias, QH),
+                               _more_arg(more, QH, dv or d), _stream()),
            "fa_prefill", *work)
 
 
@@ -1110,10 +1158,11 @@ def rows_axpy(dst: torch.Tensor, a: torch.Tensor, src: torch.Tensor, store: bool
 
 
 def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, dk: int, dv: int,
-                     window: int, scale: float, bias: Optional[torch.Tensor]) -> None:
+                     window: int, scale: float, bias: Optional[torch.Tensor], more: Optional[AttentionExtras] = None) -> None:
     """Softmax attention of a step's tokens over their requests' pages, causal or in a sliding window, with a
     learned bias by distance (float32 [QH, rows]; a head's last entry serves every greater distance) added to the scaled
-    scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv]."""
+    scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv].  more: soft cap, sink, values inside
+    the keys, output gate (AttentionExtras); the kernels whose tiles come by TMA do not take them."""
     n_dec, E = ctx.n_decode, ctx.n_entries
     dec_work = pre_work = (0.0, 0.0)
     if _profiler is not None:
@@ -1127,12 +1176,13 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
                 pairs += min(full, n * window) if window else full
                 keys += min(s0 + n, window + n) if window else s0 + n
                 toks += n
-            return 2.0 * QH * (dk + dv) * pairs, (keys * KH * (dk + dv) + toks * QH * (dk + dv)) * q.element_size()
+            stored = dk if (more is not None and more.v_in_k) else dk + dv
+            return 2.0 * QH * (dk + dv) * pairs, (keys * KH * stored + toks * QH * (dk + dv)) * q.element_size()
         dec_work, pre_work = work(0, n_dec), work(n_dec, E)
     if q.dtype != torch.bfloat16 or dk % 8 or dv % 8 or max(dk, dv) > 256:
         # 32-bit, or head sizes the tensor-core kernels do not take: the plain kernel
         paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, window, scale,
-                            work=(dec_work[0] + pre_work[0], dec_work[1] + pre_work[1]), dv=dv, bias=bias)
+                            work=(dec_work[0] + pre_work[0], dec_work[1] + pre_work[1]), dv=dv, bias=bias, more=more)
         return
     gc = fa_group_chunk(QH // KH)
     if n_dec:
@@ -1140,14 +1190,14 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
         ctas = n_dec * KH * (QH // KH // gc)
         keys = min(ctx.max_kv_len, window + 63) if window else ctx.max_kv_len
         n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-keys // 256), 16))
-        if dk == dv and tma_pages(group.page_size) and USE_TMA_ATTENTION:
+        if dk == dv and more is None and tma_pages(group.page_size) and USE_TMA_ATTENTION:
             # key size = value size: the kernel whose tiles come by TMA (up to 16 splits merge inside their cluster)
             fa_decode_tma(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
                           window, scale, work=dec_work, bias=bias)
         else:
             fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
-                      window, scale, work=dec_work, dv=dv, bias=bias)
-    if E > n_dec and dk == 128 and dv == 128 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
+                      window, scale, work=dec_work, dv=dv, bias=bias, more=more)
+    if E > n_dec and dk == 128 and dv == 128 and more is None and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
         # heads of 128: the tcgen05 kernel
         fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
                       [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, dk, group.page_size, window, scale,
@@ -1156,7 +1206,78 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
         fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, dk, group.page_size,
-                   window, scale, work=pre_work, dv=dv, bias=bias)
+                   window, scale, work=pre_work, dv=dv, bias=bias, more=more)
+
+
+def rotary_heads_append(x: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor, freq: Optional[torch.Tensor],
+                        rot: int, mag: float, kv_slot: Optional[torch.Tensor], q_out: torch.Tensor, cache: torch.Tensor,
+                        QH: int, KH: int, dk: int, dv: int, page_size: int, vmix: int = 0,
+                        lam: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None) -> None:
+    """x [T, q | k | v | ...] (float32 or bfloat16 rows): + bias (float32 over q | k | v), neighbouring dimensions (2i, 2i+1)
+    of the first `rot` of every q and k head rotated by position * freq[i] with cosine and sine times `mag`, q -> q_out
+    [T, QH, dk], k and v into the token's cache slot (pages [K: KH x page x dk | V: KH x page x dv]).  vmix 1: the values
+    (with bias) are also left in v_first (float32 [T, KH * dv]); vmix 2: v <- (1 - lam) v + lam v_first first."""
+    _need(x.stride(1) == 1 and x.shape[1] >= (QH + KH) * dk + KH * dv and q_out.is_contiguous() and cache.dtype == q_out.dtype,
+          "rotary_heads_append: x holds q | k | v, rows contiguous; q_out and the cache of one dtype")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() >= (QH + KH) * dk + KH * dv), "rotary_heads_append: a float32 bias over q | k | v")
+    _need(freq is None or (freq.dtype == torch.float32 and freq.numel() >= rot // 2), "rotary_heads_append: float32 frequencies, one a pair")
+    _need(v_first is None or (v_first.dtype == torch.float32 and v_first.is_contiguous() and v_first.numel() == x.shape[0] * KH * dv),
+          "rotary_heads_append: the first values are float32 [T, KH * dv]")
+    _need(lam is None or (lam.dtype == torch.float32 and lam.numel() == 1), "rotary_heads_append: the mixing weight is one float32 number")
+    _check(lib().rb_rotary_heads_append(_p(x), c_longlong(x.stride(0)), c_int(dt(x)), _p(bias), _p(positions), _p(freq), c_int(rot),
+                                        c_float(mag), _p(kv_slot), _p(q_out), _p(cache), c_int(dt(q_out)), c_int(x.shape[0]), c_int(QH),
+                                        c_int(KH), c_int(dk), c_int(dv), c_int(page_size), c_int(vmix), _p(lam), _p(v_first), _stream()),
+           "rotary_heads_append", 0.0, float(x.shape[0] * ((QH + KH) * dk + KH * dv) * (x.element_size() + q_out.element_size())))
+
+
+def latent_prep(x: torch.Tensor, na: int, nc: int, nr: int, wa: torch.Tensor, wc: torch.Tensor, eps: float, positions: torch.Tensor,
+                freq: Optional[torch.Tensor], rot: int, mag: float, kv_slot: Optional[torch.Tensor], a_out: torch.Tensor,
+                cache: torch.Tensor, page_size: int) -> None:
+    """x [T, a | c | r] (float32 or bfloat16 rows): a_out = rms(a) * wa; the token's cache slot (a one-head cache whose
+    pages hold keys only, [page, nc + nr]) gets rms(c) * wc and r with its first `rot` dimensions rotated in neighbouring
+    pairs.  Norm weights float32, as stored."""
+    _need(x.stride(1) == 1 and x.shape[1] >= na + nc + nr and a_out.is_contiguous() and a_out.shape[-1] == na, "latent_prep: x holds a | c | r")
+    _need(wa.dtype == torch.float32 and wc.dtype == torch.float32 and wa.numel() == na and wc.numel() == nc, "latent_prep: float32 norm weights")
+    _need(cache.dtype == a_out.dtype, "latent_prep: the cache has the activations' dtype")
+    _check(lib().rb_latent_prep(_p(x), c_longlong(x.stride(0)), c_int(dt(x)), c_int(na), c_int(nc), c_int(nr), _p(wa), _p(wc), c_float(eps),
+                                _p(positions), _p(freq), c_int(rot), c_float(mag), _p(kv_slot), _p(a_out), _p(cache), c_int(dt(a_out)),
+                                c_int(x.shape[0]), c_int(page_size), _stream()),
+           "latent_prep", 0.0, float(x.shape[0] * (na + nc + nr) * (x.element_size() + a_out.element_size())))
+
+
+def rotate_pairs(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, rot: int, mag: float) -> None:
+    """src, dst [T, H, width] views (last dimension contiguous, strides of their own, one dtype): dst = src with neighbouring
+    dimensions (2i, 2i+1) of the first `rot` rotated by position * freq[i], cosine and sine times `mag`."""
+    _need(src.dim() == 3 and dst.shape == src.shape and src.stride(2) == 1 and dst.stride(2) == 1 and src.dtype == dst.dtype,
+          "rotate_pairs: two [T, H, width] views of one dtype")
+    T, H, width = src.shape
+    _check(lib().rb_rotate_pairs(_p(src), c_longlong(src.stride(0)), c_longlong(src.stride(1)), _p(dst), c_longlong(dst.stride(0)),
+                                 c_longlong(dst.stride(1)), c_int(dt(src)), _p(positions), _p(freq), c_int(T), c_int(H), c_int(width),
+                                 c_int(rot), c_float(mag), _stream()), "rotate_pairs", 0.0, float(2 * src.numel() * src.element_size()))
+
+
+HEADS_LINEAR_GEMM_TOKENS = 32          # from this many tokens on, a bfloat16 per-head map runs as one tensor-core product a head
+
+
+def heads_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t, h, :] = w[h] x[t, h, :] for every head: x [T, H, in] and y [T, H, out] views (last dimension contiguous), w
+    [H, out, in] contiguous.  bfloat16 over many tokens: one tensor-core product per head on the strided views; else the
+    plain kernel (32-bit sums in ascending order: a token's result does not depend on the batch)."""
+    _need(x.dim() == 3 and y.dim() == 3 and w.dim() == 3 and w.is_contiguous() and x.stride(2) == 1 and y.stride(2) == 1, "heads_linear: views")
+    T, H, n_in = x.shape
+    n_out = w.shape[1]
+    _need(tuple(w.shape) == (H, n_out, n_in) and tuple(y.shape) == (T, H, n_out) and x.dtype == y.dtype, "heads_linear: shapes")
+    if T == 0:
+        return
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T >= HEADS_LINEAR_GEMM_TOKENS and n_in % 8 == 0 and \
+            x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0:
+        for h in range(H):
+            gemm_bf16(x[:, h], w[h], y[:, h])
+        return
+    _check(lib().rb_heads_linear(_p(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)), c_int(dt(x)), _p(w), c_int(dt(w)), _p(y),
+                                 c_longlong(y.stride(0)), c_longlong(y.stride(1)), c_int(T), c_int(H), c_int(n_in), c_int(n_out), _stream()),
+           f"heads_linear {n_out}x{n_in}", 2.0 * T * H * n_in * n_out,
+           float(H * n_in * n_out * w.element_size() + T * H * (n_in + n_out) * x.element_size()))
 
 
 RECURRENCE_FORMS = {"diagonal": 0, "delta_old_state": 1, "delta_gated_state": 2}

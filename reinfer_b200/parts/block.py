@@ -154,6 +154,50 @@ class OutNormBlock:
         return None
 
 
+class SandwichBlock:
+    """x += m * out_norm(mixer(norm(x)));  x += m * out_norm'(ffn(norm'(x))): a norm before every sublayer (it reads the
+    stream, as in 'prenorm') and another on what the sublayer puts out (kind `rms_out`, which also holds m and adds the
+    normalised rows to x, as in 'out_norm').  The sublayer gets a fresh float32 tensor in the place of the residual
+    (`ctx.fresh_residual`: its last product stores there, or leaves its partial sums).  Roles: mixer_norm, mixer,
+    mixer_out_norm and - together or not at all - ffn_norm, ffn, ffn_out_norm."""
+    roles = ("mixer_norm", "mixer", "mixer_out_norm")
+    hands_on_sums = True
+
+    def __init__(self, parts):
+        need_roles("sandwich", parts, self.roles)
+        self.mixer_norm, self.mixer, self.mixer_out_norm = (parts[r] for r in self.roles)
+        self.ffn_norm, self.ffn, self.ffn_out_norm = parts.get("ffn_norm"), parts.get("ffn"), parts.get("ffn_out_norm")
+        have = [x is not None for x in (self.ffn_norm, self.ffn, self.ffn_out_norm)]
+        if any(have) and not all(have):
+            raise ValueError("block 'sandwich': a feed-forward comes with the norm before it and the norm behind it")
+        for n in (self.mixer_out_norm, self.ffn_out_norm):
+            if n is not None and not hasattr(n, "add"):
+                raise ValueError("block 'sandwich' needs output norms that add a sublayer's normalised output to the stream (kind 'rms_out')")
+
+    @staticmethod
+    def _sublayer(ctx, x, pre, part, post, run, delta=None) -> None:
+        xn = _norm(pre, part, ctx, x, delta)
+        y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        ctx.fresh_residual, ctx.norm_ahead = True, None
+        try:
+            left = run(xn, y)
+            if left is None and ctx.fresh_residual and x.shape[0]:
+                raise RuntimeError("block 'sandwich': the sublayer did not hand over its output (parts.linear.matmul_into_residual)")
+        finally:
+            ctx.fresh_residual = False
+        post.add(ctx, x, y if left is None else left, None)
+
+    def forward(self, ctx, x, cache, delta=None):
+        if isinstance(delta, PreparedRows):
+            delta = None                            # the product that made them has completed x already
+        self._sublayer(ctx, x, self.mixer_norm, self.mixer, self.mixer_out_norm,
+                       lambda h, y: self.mixer.forward(ctx, h, y, cache), delta)
+        if self.ffn is not None:
+            self._sublayer(ctx, x, self.ffn_norm, self.ffn, self.ffn_out_norm, lambda h, y: self.ffn.forward(ctx, h, y))
+        return None
+
+
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "out_norm", OutNormBlock)
 register_part("block", "prenorm_mixer", PreNormMixerBlock)

@@ -1,6 +1,9 @@
 """RMSNorm: x * (1/sqrt(mean(x^2) + eps)) * w, eps inside the root, plain weight,
 32-bit arithmetic (crates/cuda/kernels/dense_kernels.cu:59-88; the residual-fused
-form :257-296)."""
+form :257-296).  Two options serve checkpoints of another convention: `unit_offset` (the tensor
+holds the weight's distance from one: the factor is 1 + w) and `gain` (a constant on the output, for
+instance a scale on the logits folded into the last norm); either makes the bound weight float32,
+formed once at load, so that 1 + w keeps the digits a 16-bit sum would drop."""
 from __future__ import annotations
 
 import torch
@@ -10,20 +13,33 @@ from ..weights.params import ParamSpec
 from .base import Norm, PreparedRows, RowScaled, register_part
 
 
+def effective_weight(w: torch.Tensor, unit_offset: bool, gain: float) -> torch.Tensor:
+    """The factor a norm multiplies with: the stored tensor, or (1 + w) * gain as float32."""
+    if not unit_offset and gain == 1.0:
+        return w
+    f = w.float()
+    if unit_offset:
+        f = f + 1.0
+    if gain != 1.0:
+        f = f * gain
+    return f.contiguous()
+
+
 class RMSNorm(Norm):
     adds_partial_sums = True            # delta may be a stack [S, rows, width] of partial sums
     leaves_row_scale = True             # forward(..., scaled_ok=True) may return a RowScaled
 
-    def __init__(self, width: int, eps: float, weight_name: str = "weight"):
+    def __init__(self, width: int, eps: float, weight_name: str = "weight", unit_offset: bool = False, gain: float = 1.0):
         """weight_name: the local name of the weight ("" where the part's prefix is the tensor's whole name)."""
         self.width, self.eps, self.weight_name = int(width), float(eps), str(weight_name)
+        self.unit_offset, self.gain = bool(unit_offset), float(gain)
         self.weight = None
 
     def param_specs(self):
-        return {self.weight_name: ParamSpec((self.width,), init="norm")}
+        return {self.weight_name: ParamSpec((self.width,), init="norm_offset" if self.unit_offset else "norm")}
 
     def bind(self, tensors):
-        self.weight = tensors[self.weight_name]
+        self.weight = effective_weight(tensors[self.weight_name], self.unit_offset, self.gain)
 
     def prepared_by(self, ctx, a, w, residual):
         """residual += a w^T by a product that also makes this norm's rows of the new residual (a decode step's few
@@ -60,15 +76,16 @@ class ResidualOutNorm(Norm):
     product left.  `add` can leave the new x once more, rounded to bfloat16, for the sublayer that reads it next."""
     adds_partial_sums = True
 
-    def __init__(self, width: int, eps: float, mult: float = 1.0, weight_name: str = "weight"):
+    def __init__(self, width: int, eps: float, mult: float = 1.0, weight_name: str = "weight", unit_offset: bool = False):
         self.width, self.eps, self.mult, self.weight_name = int(width), float(eps), float(mult), str(weight_name)
+        self.unit_offset = bool(unit_offset)
         self.weight = None
 
     def param_specs(self):
-        return {self.weight_name: ParamSpec((self.width,), init="norm")}
+        return {self.weight_name: ParamSpec((self.width,), init="norm_offset" if self.unit_offset else "norm")}
 
     def bind(self, tensors):
-        self.weight = tensors[self.weight_name]
+        self.weight = effective_weight(tensors[self.weight_name], self.unit_offset, 1.0)
 
     def add(self, ctx, x, y, rounded=None, extra=None) -> None:
         """extra = (a [rows], src [rows, width]): a[r] * src[r] joins y[r] before the norm."""

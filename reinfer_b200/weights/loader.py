@@ -112,6 +112,8 @@ def random_state(expected: Mapping[str, ParamSpec], seed: int, dtype: torch.dtyp
             out[name] = torch.zeros(spec.shape, dtype=dtype, device=dev)
         elif spec.init == "norm":
             out[name] = rnd.normal(spec.shape, seed, name, 1.0, 0.05, dtype, dev)
+        elif spec.init == "norm_offset":            # a norm weight stored as its distance from one
+            out[name] = rnd.normal(spec.shape, seed, name, 0.0, 0.05, dtype, dev)
         else:
             out[name] = rnd.normal(spec.shape, seed, name, 0.0, spec.std, dtype, dev)
     return out

@@ -9,7 +9,7 @@ from typing import Tuple
 @dataclass(frozen=True)
 class ParamSpec:
     shape: Tuple[int, ...]
-    # "matrix"/"table": N(0, 0.02); "norm": 1 + N(0, 0.05); "zeros"; "int_table": uniform ints
+    # "matrix"/"table": N(0, std); "norm": 1 + N(0, 0.05); "norm_offset": N(0, 0.05); "zeros"; "int_table": uniform ints
     init: str = "matrix"
     kind: str = "float"            # "float" follows the dtype rule of the loader; "int" is kept as int32
     std: float = 0.02
