@@ -337,6 +337,25 @@ def damadra_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 327
             "norm": {"eps": 1e-6}, "residual_mult": 0.4, "layers": out}
 
 
+def molitar_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
+                  kv_rank: int = 192, rot_dim: int = 64) -> Dict:
+    """A Molitar config.json at layer sizes that resemble a real model's: `layers` layers of which every third (the
+    second, the fifth, ...) is a gated attention layer (heads of `head_dim` over heads / 4 key/value heads, half of each
+    head rotated, a soft cap of 30, a sink, value mixing and an output gate) and the others latent attention layers
+    (heads of `head_dim` + `rot_dim`, values of `head_dim`, a query bottleneck of 3/4 of the width and a latent of
+    `kv_rank`: a token's cached row is kv_rank + rot_dim numbers, stretched rotation), all with dense feed-forwards."""
+    kv = kv_heads or max(1, heads // 4)
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": 3 * width // 4, "kv_rank": kv_rank,
+              "scale": (head_dim + rot_dim) ** -0.5,
+              "rot": {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    gated = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "softcap": 30.0, "v_mix": True,
+             "rot": {"base": 1e6, "dims": head_dim // 2}}
+    out = [{"type": "attention", "mixer": gated, "mlp": {"kind": "dense", "ff": ff}} if i % 3 == 1 else
+           {"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]
+    return {"architecture": "Molitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.4, "logit_scale": 0.5,
+            "layers": out}
+
+
 def qwen3_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
                 positions: int = 8192) -> Dict:
     """The closest existing design at the same layer sizes."""
