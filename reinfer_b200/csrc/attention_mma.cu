@@ -100,26 +100,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D> struct FaSmem {
     static constexpr int STRIDE = D * 2 + 16;                 // bytes per row: 16 bytes of padding keep ldmatrix conflict-free
     static constexpr int TILE = FA_BN * STRIDE;               // one K or V tile
-    static constexpr int STAGE = 2 * TILE;
+    static constexpr int STAGE = 2 * TILE;                    // keys and values
+    static constexpr int STAGE_VK = TILE;                     // values inside the keys: the key tile serves both products
 };
+template <int D, bool VK> __host__ __device__ constexpr int fa_stage() { return VK ? FaSmem<D>::STAGE_VK : FaSmem<D>::STAGE; }
 
 // Copy keys [k0, k0+64) of kv head `kh` (K and V) of the request whose block-table row is `bt`
 // into one stage.  Rows at or beyond `kv_end`, rows in pages that were given back (id < 0) and
 // the padding dims d..D are zero-filled, so nothing that is not the request's own data is read.
 // A thread always copies the same 16-byte column of rows r0, r0 + RPI, ...; with a page size that
-// is a power of two (page_shift >= 0) the page of a row costs a shift and a mask.
-template <int D>
+// is a power of two (page_shift >= 0) the page of a row costs a shift and a mask.  VK: the values are the first dv
+// columns of the key rows and the stage holds the key tile only.
+template <int D, bool VK>
 __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs& a, const int* bt, int kh, int k0, int kv_end) {
     constexpr int CPR = D / 8;                                // 16-byte chunks per row
     constexpr int RPI = FA_THREADS / CPR;                     // rows per pass over the tile
     static_assert(FA_THREADS % CPR == 0 && FA_BN % RPI == 0, "tile shape");
     const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
     const bool kcol_ok = c * 8 < a.d, vcol_ok = c * 8 < a.dv;
-    const size_t head_stride = (size_t)a.page_size * a.d, vhead_stride = a.v_in_k ? head_stride : (size_t)a.page_size * a.dv;
-    const size_t page_stride = a.v_in_k ? (size_t)a.KH * head_stride : (size_t)a.KH * (head_stride + vhead_stride);
-    const int v_row = a.v_in_k ? a.d : a.dv;
+    const size_t head_stride = (size_t)a.page_size * a.d, vhead_stride = VK ? head_stride : (size_t)a.page_size * a.dv;
+    const size_t page_stride = VK ? (size_t)a.KH * head_stride : (size_t)a.KH * (head_stride + vhead_stride);
+    const int v_row = VK ? a.d : a.dv;
     const bf16* kbase = a.cache + (size_t)kh * head_stride + c * 8;
-    const bf16* vbase = a.cache + (a.v_in_k ? 0 : (size_t)a.KH * head_stride) + (size_t)kh * vhead_stride + c * 8;
+    const bf16* vbase = a.cache + (VK ? 0 : (size_t)a.KH * head_stride) + (size_t)kh * vhead_stride + c * 8;
     unsigned char* dst0 = stage + r0 * FaSmem<D>::STRIDE + c * 16;
 #pragma unroll
     for (int i = 0; i < FA_BN / RPI; ++i) {
@@ -139,7 +142,7 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
         }
         unsigned char* dst = dst0 + i * RPI * FaSmem<D>::STRIDE;
         cp_async16(dst, ksrc, kbytes);
-        cp_async16(dst + FaSmem<D>::TILE, vsrc, vbytes);
+        if (!VK) cp_async16(dst + FaSmem<D>::TILE, vsrc, vbytes);
     }
 }
 
@@ -152,7 +155,7 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
                                         float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                         bool pen = false, float pa0 = 0.0f, float pb0 = 0.0f, float pa1 = 0.0f, float pb1 = 0.0f,
                                         const float* bias0 = nullptr, const float* bias1 = nullptr, int bias_stride = 0, int bias_last = 0,
-                                        float cap_log2 = 0.0f, float scale_over_cap = 0.0f) {
+                                        float cap_log2 = 0.0f, float scale_over_cap = 0.0f, int dv_cols = D) {
     constexpr int STRIDE = FaSmem<D>::STRIDE;
     const int lane = threadIdx.x & 31;
     float s[NT][4];
@@ -229,6 +232,7 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
         const uint32_t pa[4] = {p[2 * kk][0], p[2 * kk][1], p[2 * kk + 1][0], p[2 * kk + 1][1]};
 #pragma unroll
         for (int dp = 0; dp < D / 16; ++dp) {
+            if (dp * 16 >= dv_cols) continue;                  // columns beyond the value heads' size stay zero (the same for the whole CTA)
             uint32_t vb[4];
             ldsm_x4_trans(vb, sV + (koff + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + (dp * 16 + 8 * (lane >> 4)) * 2);
             mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
@@ -252,10 +256,11 @@ __device__ __forceinline__ void fa_load_q(unsigned char* sQ, const FaArgs& a, in
 }
 
 // ------------------------------------------------------------------------ prefill
-template <int D>
+template <int D, bool VK>
 __global__ void __launch_bounds__(FA_THREADS)
 fa_prefill_kernel(const FaArgs a) {
     constexpr int NST = 2;
+    constexpr int STAGE = fa_stage<D, VK>();
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_trigger(); pdl_wait();
     unsigned char* sQ = smem;
@@ -305,19 +310,19 @@ fa_prefill_kernel(const FaArgs a) {
     for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-    fa_load_tile<D>(stages, a, bt, kh, t_begin * FA_BN, kv_end);
+    fa_load_tile<D, VK>(stages, a, bt, kh, t_begin * FA_BN, kv_end);
     cp_async_commit();
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) % NST;
         cp_async_wait<0>();
         __syncthreads();                                       // tile t has landed; tile t-1 is no longer read
-        if (t + 1 < t_end) fa_load_tile<D>(stages + ((buf + 1) % NST) * FaSmem<D>::STAGE, a, bt, kh, (t + 1) * FA_BN, kv_end);
+        if (t + 1 < t_end) fa_load_tile<D, VK>(stages + ((buf + 1) % NST) * STAGE, a, bt, kh, (t + 1) * FA_BN, kv_end);
         cp_async_commit();
         if (t < warp_t_end) {
-            const unsigned char* sK = stages + buf * FaSmem<D>::STAGE;
-            fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, sK + FaSmem<D>::TILE, 0, t * FA_BN,
+            const unsigned char* sK = stages + buf * STAGE;
+            fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, VK ? sK : sK + FaSmem<D>::TILE, 0, t * FA_BN,
                                   pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
-                                  bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap);
+                                  bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap, a.dv);
         }
     }
     cp_async_wait<0>();
@@ -357,9 +362,10 @@ fa_prefill_kernel(const FaArgs a) {
 }
 
 // ------------------------------------------------------------------------- decode
-template <int D, int NST>
+template <int D, int NST, bool VK>
 __global__ void __launch_bounds__(FA_THREADS)
 fa_decode_kernel(const FaArgs a) {
+    constexpr int STAGE = fa_stage<D, VK>();
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_trigger(); pdl_wait();
     unsigned char* sQ = smem;                                  // 16 rows
@@ -394,7 +400,7 @@ fa_decode_kernel(const FaArgs a) {
 
 #pragma unroll
     for (int i = 0; i < NST - 1; ++i) {
-        if (t_begin + i < t_end) fa_load_tile<D>(stages + i * FaSmem<D>::STAGE, a, bt, kh, (t_begin + i) * FA_BN, kv_end);
+        if (t_begin + i < t_end) fa_load_tile<D, VK>(stages + i * STAGE, a, bt, kh, (t_begin + i) * FA_BN, kv_end);
         cp_async_commit();
     }
     for (int t = t_begin; t < t_end; ++t) {
@@ -402,11 +408,11 @@ fa_decode_kernel(const FaArgs a) {
         cp_async_wait<NST - 2>();
         __syncthreads();
         if (t + NST - 1 < t_end)
-            fa_load_tile<D>(stages + ((it + NST - 1) % NST) * FaSmem<D>::STAGE, a, bt, kh, (t + NST - 1) * FA_BN, kv_end);
+            fa_load_tile<D, VK>(stages + ((it + NST - 1) % NST) * STAGE, a, bt, kh, (t + NST - 1) * FA_BN, kv_end);
         cp_async_commit();
-        const unsigned char* sK = stages + (it % NST) * FaSmem<D>::STAGE;
-        fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
-                      bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap);
+        const unsigned char* sK = stages + (it % NST) * STAGE;
+        fa_tile<D, 2>(sQ, sK, VK ? sK : sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
+                      bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap, a.dv);
     }
     cp_async_wait<0>();
     __syncthreads();                                           // the stages are free: reuse them for the merge
@@ -498,29 +504,38 @@ static int fa_group_chunk(int G) {                             // largest diviso
     return 1;
 }
 
-template <int D>
-static int fa_launch_prefill(const FaArgs& a, int n_tiles, cudaStream_t s) {
-    const size_t smem = (size_t)FA_BM * FaSmem<D>::STRIDE + 2 * FaSmem<D>::STAGE;
+template <int D, bool VK>
+static int fa_launch_prefill_as(const FaArgs& a, int n_tiles, cudaStream_t s) {
+    const size_t smem = (size_t)FA_BM * FaSmem<D>::STRIDE + 2 * fa_stage<D, VK>();
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(fa_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(fa_prefill_kernel<D, VK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    return rb_launch(fa_prefill_kernel<D>, dim3(n_tiles, a.KH * a.chunks), dim3(FA_THREADS), smem, s, a);
+    return rb_launch(fa_prefill_kernel<D, VK>, dim3(n_tiles, a.KH * a.chunks), dim3(FA_THREADS), smem, s, a);
 }
-template <int D, int NST>
-static int fa_launch_decode(const FaArgs& a, cudaStream_t s) {
-    const size_t pipe = (size_t)NST * FaSmem<D>::STAGE;
+template <int D>
+static int fa_launch_prefill(const FaArgs& a, int n_tiles, cudaStream_t s) {
+    return a.v_in_k ? fa_launch_prefill_as<D, true>(a, n_tiles, s) : fa_launch_prefill_as<D, false>(a, n_tiles, s);
+}
+template <int D, int NST, bool VK>
+static int fa_launch_decode_as(const FaArgs& a, cudaStream_t s) {
+    const size_t pipe = (size_t)NST * fa_stage<D, VK>();
     const size_t merge = (size_t)FA_WARPS * 16 * (D + 2) * sizeof(float);
     const size_t smem = 16 * FaSmem<D>::STRIDE + (pipe > merge ? pipe : merge);
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<D, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<D, NST, VK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    return rb_launch(fa_decode_kernel<D, NST>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FA_THREADS), smem, s, a);
+    return rb_launch(fa_decode_kernel<D, NST, VK>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FA_THREADS), smem, s, a);
+}
+// (a key tile alone leaves room for one more stage)
+template <int D, int NST>
+static int fa_launch_decode(const FaArgs& a, cudaStream_t s) {
+    return a.v_in_k ? fa_launch_decode_as<D, NST + 1, true>(a, s) : fa_launch_decode_as<D, NST, false>(a, s);
 }
 
 // What the soft cap, the sink, values inside the keys and the gate add to the arguments.

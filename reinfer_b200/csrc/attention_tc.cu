@@ -41,6 +41,8 @@
 // (128 threads x 80) must cover what the rows take (256 threads x 40), for the registers come from the CTA's own
 // allocation (384 x 168) and a request for more than it holds waits for ever.
 //
+// Options on top: a distance penalty, a learned bias by distance, chunks, a soft cap on the scores (before penalty and
+// bias), a sink in the denominator and a sigmoid gate on the output - each skipped when not asked for.
 // Head size 128, page size a power of two >= 8.  Every wait is bounded (2 s); a CTA that gives up raises the
 // error word, lets its copies land, frees its tensor memory and leaves; CTAs that start after that leave at once.
 #define RB_UNIT 3
@@ -81,6 +83,14 @@ struct FcArgs {
     // the scaled score; null: none).  Its last column stands for every greater distance.
     const float* bias;
     int bias_last;
+    // A soft cap: score <- cap tanh(score / cap) on the scaled score; here in units of the raw score (cap / scale), with
+    // 2 log2(e) / that for the exponential the tanh is made of (0: none).
+    float cap_raw, cap_arg;
+    // A sink: one more term exp(sink[h]) in a row's denominator, with no key and no value (null: none).
+    const float* sink;
+    // An output gate: out *= sigmoid(gate[t * gate_stride + h * 128 + i]) (null: none).
+    const float* gate;
+    long long gate_stride;
 };
 
 struct FcShared {
@@ -447,6 +457,15 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->s_free[t][b]));          // this buffer may take the scores of tile it + 2
+            if (a.cap_raw > 0.0f) {
+                // tanh z = 1 - 2 / (e^(2z) + 1): one exponential and one reciprocal of the special-function unit, exact
+                // at both ends (e = inf gives 1, e = 0 gives -1); the error is an absolute 2^-23 or so of the cap
+#pragma unroll
+                for (int j = 0; j < FC_BN; ++j) {
+                    const float e2 = fc_ex2(__uint_as_float(sr[j]) * a.cap_arg);
+                    sr[j] = __float_as_uint(fmaf(-a.cap_raw, __fdividef(2.0f, e2 + 1.0f), a.cap_raw));
+                }
+            }
             if (pen) {                                             // (places beyond the row's position are replaced below)
                 const float dist0 = (float)(pos - k0);
 #pragma unroll
@@ -564,8 +583,10 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         if (ok && n_tiles > 0 && !*abort_flag) {
             // (the loads from tensor memory are the whole warp's: every lane takes part, only live rows store)
             tc_fence_after();
+            if (a.sink && m != -INFINITY) l += fc_ex2(fmaf(a.sink[head0 + row % a.Gc], 1.4426950408889634f, -m));   // in the scale of l
             const float inv = l > 0.0f ? a.out_scale / l : 0.0f;
             bf16* dst = a.out + ((size_t)(tok_base + (live ? ti : 0)) * a.QH + head0 + row % a.Gc) * FC_D;
+            const float* grow = (a.gate && live) ? a.gate + (size_t)(tok_base + ti) * a.gate_stride + (size_t)(head0 + row % a.Gc) * FC_D : nullptr;
 #pragma unroll
             for (int c = 0; c < FC_D / 32; ++c) {
                 uint32_t ov[32];
@@ -573,6 +594,10 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
                 tc_ld16(lane_base + o_col + (uint32_t)(c * 32 + 16), ov + 16);
                 tc_ld_wait();
                 if (!live) continue;
+                if (grow) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) / (1.0f + expf(-grow[c * 32 + j])));
+                }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     uint4 pk;
@@ -611,9 +636,11 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
                                 const int* kv_len, void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d,
                                 int page_size, int max_pages, int window, float scale, int chunk, const float* r1, const float* r2,
-                                float out_scale, const float* bias, int bias_rows, void* stream) {
+                                float out_scale, const float* bias, int bias_rows, float softcap, const float* sink,
+                                const float* gate, long long gate_stride, void* stream) {
     if (n_entries <= 0 || n_tiles <= 0) return 0;
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
+    if (softcap < 0.0f || (softcap > 0.0f && !(scale > 0.0f))) RB_REFUSE("attention (tcgen05): a soft cap of %g at scale %g", (double)softcap, (double)scale);
     if (bias && bias_rows <= 0) RB_REFUSE("attention: a distance bias of %d rows", bias_rows);
     if (d != FC_D) RB_REFUSE("attention (tcgen05): head_dim %d, only 128 is built", d);
     // a chunk that starts inside a key tile would leave the tile's first keys to pages that may have gone back to the pool
@@ -632,6 +659,8 @@ extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_
     a.scale_log2 = scale * 1.4426950408889634f;
     a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
     a.bias = bias; a.bias_last = bias_rows - 1;
+    if (softcap > 0.0f) { a.cap_raw = softcap / scale; a.cap_arg = 2.0f * 1.4426950408889634f * scale / softcap; }
+    a.sink = sink; a.gate = gate; a.gate_stride = gate_stride;
     CUtensorMap map;
     if (rb_tensor_map_kv_pages(cache, num_pages, KH, page_size, &map)) return -1;
     constexpr size_t smem = (size_t)FC_NST * FC_STAGE + FC_TILES * 4 * FC_QHALF + sizeof(FcShared) + 1024;

@@ -539,17 +539,22 @@ def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n
 
 def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, q_lens,
                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-                  chunk: int = 0, penalty=None, out_scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
+                  chunk: int = 0, penalty=None, out_scale: float = 1.0, bias: Optional[torch.Tensor] = None,
+                  more: Optional["AttentionExtras"] = None) -> None:
     """Paged causal flash attention on the tcgen05 tensor cores (scores and the weighted sum in tensor memory):
     head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host).  chunk (a multiple
-    of 64), penalty = (r1, r2), out_scale and bias as in paged_attention_ref."""
+    of 64), penalty = (r1, r2), out_scale and bias as in paged_attention_ref; more: soft cap, sink and gate (not values
+    inside the keys)."""
+    _need(more is None or not more.v_in_k, "fa_prefill_tc: the pages hold keys and values")
+    extras = (more or _NO_EXTRAS).flat(QH, d)
     gc = int(lib().rb_fa_prefill_tc_group(c_int(QH), c_int(KH)))
     tpt = int(lib().rb_fa_prefill_tc_rows()) // gc              # tokens that one CTA takes
     n_tiles = sum(-(-int(n) // tpt) for n in q_lens)
     _check(lib().rb_fa_prefill_tc(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
                                   c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(chunk),
-                                  *_penalty_args(penalty, QH), c_float(out_scale), *_bias_args(bias, QH), _stream()),
+                                  *_penalty_args(penalty, QH), c_float(out_scale), *_bias_args(bias, QH), extras[0], extras[1],
+                                  extras[3], extras[4], _stream()),
            "fa_prefill_tc", *work)
 
 
@@ -1162,7 +1167,8 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
     """Softmax attention of a step's tokens over their requests' pages, causal or in a sliding window, with a
     learned bias by distance (float32 [QH, rows]; a head's last entry serves every greater distance) added to the scaled
     scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv].  more: soft cap, sink, values inside
-    the keys, output gate (AttentionExtras); the kernels whose tiles come by TMA do not take them."""
+    the keys, output gate (AttentionExtras); the decode kernel whose tiles come by TMA does not take them, the tcgen05
+    prefill kernel takes all but values inside the keys."""
     n_dec, E = ctx.n_decode, ctx.n_entries
     dec_work = pre_work = (0.0, 0.0)
     if _profiler is not None:
@@ -1189,7 +1195,8 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
         # the keys a token sees (all before it, or its window) are split over CTAs while that fills the device
         ctas = n_dec * KH * (QH // KH // gc)
         keys = min(ctx.max_kv_len, window + 63) if window else ctx.max_kv_len
-        n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-keys // 256), 16))
+        per = 256 if ctas * -(-keys // 256) >= DECODE_SLOTS // 2 else 128     # few heads and requests: finer splits fill the device
+        n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-keys // per), 16))
         if dk == dv and more is None and tma_pages(group.page_size) and USE_TMA_ATTENTION:
             # key size = value size: the kernel whose tiles come by TMA (up to 16 splits merge inside their cluster)
             fa_decode_tma(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
@@ -1197,11 +1204,12 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
         else:
             fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
                       window, scale, work=dec_work, dv=dv, bias=bias, more=more)
-    if E > n_dec and dk == 128 and dv == 128 and more is None and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
+    if E > n_dec and dk == 128 and dv == 128 and (more is None or not more.v_in_k) and USE_TC_ATTENTION and USE_TMA_ATTENTION and \
+            tma_pages(group.page_size):
         # heads of 128: the tcgen05 kernel
         fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
                       [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, dk, group.page_size, window, scale,
-                      work=pre_work, bias=bias)
+                      work=pre_work, bias=bias, more=more)
     elif E > n_dec:
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
@@ -1256,28 +1264,35 @@ def rotate_pairs(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, 
                                  c_int(rot), c_float(mag), _stream()), "rotate_pairs", 0.0, float(2 * src.numel() * src.element_size()))
 
 
-HEADS_LINEAR_GEMM_TOKENS = 32          # from this many tokens on, a bfloat16 per-head map runs as one tensor-core product a head
-
-
-def heads_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
-    """y[t, h, :] = w[h] x[t, h, :] for every head: x [T, H, in] and y [T, H, out] views (last dimension contiguous), w
-    [H, out, in] contiguous.  bfloat16 over many tokens: one tensor-core product per head on the strided views; else the
-    plain kernel (32-bit sums in ascending order: a token's result does not depend on the batch)."""
+def heads_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, tail=None) -> None:
+    """y[t, h, :n_out] = w[h] x[t, h, :n_in] for every head: x [T, H, n_in (+ tail)] and y [T, H, n_out (+ tail)] views (last
+    dimension contiguous), w [H, n_out, n_in] contiguous.  tail = (positions, freq, rot, mag): the columns of x behind
+    the head's inputs go behind the head's outputs in y, their first `rot` dimensions rotated in neighbouring pairs.
+    bfloat16: one tensor-core launch for all heads (tail included); else the plain kernel (32-bit sums in ascending order)
+    and `rotate_pairs`.  Either way a token's result does not depend on the batch."""
     _need(x.dim() == 3 and y.dim() == 3 and w.dim() == 3 and w.is_contiguous() and x.stride(2) == 1 and y.stride(2) == 1, "heads_linear: views")
-    T, H, n_in = x.shape
-    n_out = w.shape[1]
-    _need(tuple(w.shape) == (H, n_out, n_in) and tuple(y.shape) == (T, H, n_out) and x.dtype == y.dtype, "heads_linear: shapes")
+    T, H = x.shape[0], x.shape[1]
+    n_out, n_in = w.shape[1], w.shape[2]
+    n_tail = x.shape[2] - n_in
+    _need(w.shape[0] == H and n_tail >= 0 and tuple(y.shape) == (T, H, n_out + n_tail) and x.dtype == y.dtype and
+          (n_tail == 0 or tail is not None), "heads_linear: shapes")
     if T == 0:
         return
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T >= HEADS_LINEAR_GEMM_TOKENS and n_in % 8 == 0 and \
-            x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0:
-        for h in range(H):
-            gemm_bf16(x[:, h], w[h], y[:, h])
+    positions, freq, rot, mag = tail if (tail is not None and n_tail) else (None, None, 0, 1.0)
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and n_in % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and \
+            x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+        _check(lib().rb_heads_linear_mma(_p(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)), _p(w), _p(y), c_longlong(y.stride(0)),
+                                         c_longlong(y.stride(1)), c_int(T), c_int(H), c_int(n_in), c_int(n_out), c_int(n_tail), c_int(rot),
+                                         _p(positions), _p(freq), c_float(mag), _stream()),
+               f"heads_linear {n_out}x{n_in}", 2.0 * T * H * n_in * n_out,
+               float(H * n_in * n_out * 2 + T * H * (n_in + n_out + 2 * n_tail) * 2))
         return
     _check(lib().rb_heads_linear(_p(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)), c_int(dt(x)), _p(w), c_int(dt(w)), _p(y),
                                  c_longlong(y.stride(0)), c_longlong(y.stride(1)), c_int(T), c_int(H), c_int(n_in), c_int(n_out), _stream()),
            f"heads_linear {n_out}x{n_in}", 2.0 * T * H * n_in * n_out,
            float(H * n_in * n_out * w.element_size() + T * H * (n_in + n_out) * x.element_size()))
+    if n_tail:
+        rotate_pairs(x[:, :, n_in:], y[:, :, n_out:], positions, freq, rot, mag)
 
 
 RECURRENCE_FORMS = {"diagonal": 0, "delta_old_state": 1, "delta_gated_state": 2}

@@ -15,8 +15,8 @@ rotation is a registered position encoding (kind `rope_pairs`: neighbouring pair
 `scale` is used as given.
 
 Launches: fused projection [W_dq; W_dkv] -> `latent_prep` (both norms, the shared key's rotation, the cache store) ->
-W_uq -> per-head W_uk^T on the plain part (`heads_linear`) and rotation of the rotated part -> attention ->
-per-head W_uv (`heads_linear`) -> output projection.  The bottleneck rows reach the norms as 32-bit sums.
+W_uq -> per-head W_uk^T on the plain part with the rotation of the rotated part behind it (`heads_linear`, one launch for
+all heads) -> attention -> per-head W_uv (`heads_linear`) -> output projection.  The bottleneck rows reach the norms as 32-bit sums.
 """
 from __future__ import annotations
 
@@ -89,9 +89,7 @@ class LatentAttention(Mixer):
                         g.kv_slot if cache.write else None, a, cache.kv, g.page_size)
         q = matmul(ctx, a, self.w_uq).view(T, H, dn + dr)
         qf = torch.empty((T, H, rkv + dr), dtype=act, device=dev)                  # [W_uk^T q_plain | rot(q_rot)] per head
-        ops.heads_linear(q[:, :, :dn], self.w_absorb, qf[:, :, :rkv])
-        if dr:
-            ops.rotate_pairs(q[:, :, dn:], qf[:, :, rkv:], ctx.positions, freq, self.rot, mag)
+        ops.heads_linear(q, self.w_absorb, qf, tail=(ctx.positions, freq, self.rot, mag))     # the rotated part rides along
         lat = torch.empty((T, H, rkv), dtype=act, device=dev)
         ops.biased_attention(ctx, qf, cache.kv, g, lat, H, 1, rkv + dr, rkv, 0, self.scale, None,
                              more=ops.AttentionExtras(v_in_k=True))

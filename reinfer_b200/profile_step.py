@@ -46,7 +46,7 @@ def main(argv=None) -> int:
     from .engine import Engine, StepEntry
 
     _raw, cfg, _full = measure.load_shape(a.shape, a.layers)
-    a.layers = int(_raw["num_hidden_layers"])
+    a.layers = int(_raw["num_hidden_layers"]) if "num_hidden_layers" in _raw else len(_raw.get("layers", []))   # (designs that list their layers)
     if a.mode == "gemm-tiles":
         return gemm_tiles(ops, torch, _raw, a.prefill_tokens)
     B, N = a.batch, a.context

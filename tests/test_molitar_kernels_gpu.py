@@ -195,6 +195,33 @@ def test_every_head_has_its_own_matrix(dtype, T, H, n_in, n_out):
     assert (out[:, :, :8] == 9.0).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,n_in,n_out,n_tail,rot_dims", [(1, 4, 16, 40, 8, 8), (70, 3, 24, 13, 6, 4), (130, 16, 128, 200, 64, 64),
+                                                          (9, 2, 72, 64, 16, 0), (65, 5, 8, 136, 10, 10)])
+def test_heads_map_carries_a_rotated_tail_and_ignores_the_batch(dtype, T, H, n_in, n_out, n_tail, rot_dims):
+    """The columns behind a head's inputs go behind its outputs, rotated by position; a token alone gives the very bits it
+    gives among the others (rows beyond a tile's end, tiles of unequal fill)."""
+    from reinfer_b200 import ops
+    from reinfer_b200.parts.rope import PairRotary
+    g = _gen(T * 3 + n_in + n_tail)
+    rot = {"base": 1000.0, "dims": rot_dims, "scaling": None}
+    enc = PairRotary(dims=rot_dims, base=rot["base"], scaling=None)
+    enc.prepare(DEV)
+    x = torch.randn(T, H, n_in + n_tail, generator=g).to(dtype)
+    w = (torch.randn(H, n_out, n_in, generator=g) / math.sqrt(n_in)).to(dtype)
+    positions = torch.randint(0, 3000, (T,), generator=g, dtype=torch.int32)
+    ref = torch.cat([torch.einsum("thi,hoi->tho", x[:, :, :n_in].double(), w.double()),
+                     plain.rotate_pairs(x[:, :, n_in:].float(), positions, rot).double()], dim=2)   # angles in 32-bit, as the design has them
+    y = torch.empty(T, H, n_out + n_tail, dtype=dtype, device=DEV)
+    tail = (positions.to(DEV), enc.freq, rot_dims, enc.magnitude)
+    ops.heads_linear(x.to(DEV), w.to(DEV), y, tail=tail)
+    assert (y.double().cpu() - ref).abs().max() <= (1e-5 if dtype == torch.float32 else 1e-2) * ref.abs().max()
+    for t in sorted({0, T // 2, T - 1}):
+        one = torch.empty(1, H, n_out + n_tail, dtype=dtype, device=DEV)
+        ops.heads_linear(x[t:t + 1].to(DEV), w.to(DEV), one, tail=(positions[t:t + 1].to(DEV), enc.freq, rot_dims, enc.magnitude))
+        assert torch.equal(one[0], y[t])
+
+
 # ------------------------------------------------------------------ attention: soft cap, sink, values inside the keys, gate
 def _paged(k, v, page, KH, dk, dv, pages_total, table):
     """Scatter k [n, KH, dk] and v [n, KH, dv] (None: the pages hold keys only) into a cache [pages][K | V] by a block table."""
@@ -232,6 +259,10 @@ def _ctx(lo, hi):
     (6, 3, 16, 24, 8, 3.0, True, True, False),          # everything at once, value heads wider than the keys'
     (2, 1, 10, 6, 4, 2.5, True, True, False),           # sizes no tensor-core kernel takes
     (4, 2, 128, 64, 64, 15.0, True, True, False),
+    (8, 2, 128, 128, 16, 12.0, True, True, False),      # heads of 128: prompts go to the tcgen05 kernel
+    (4, 4, 128, 128, 64, 0.0, True, False, False),
+    (4, 1, 128, 128, 16, 8.0, False, False, False),
+    (2, 2, 128, 128, 8, 0.0, False, True, False),
     (4, 2, 96, 48, 16, 0.0, True, False, False),        # a sink alone
     (8, 1, 32, 16, 16, 4.0, False, False, False),       # a cap alone
     (4, 4, 64, 64, 64, 0.0, False, True, False),        # a gate alone
