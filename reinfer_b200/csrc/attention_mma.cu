@@ -267,8 +267,9 @@ fa_prefill_kernel(const FaArgs a) {
     unsigned char* stages = smem + FA_BM * FaSmem<D>::STRIDE;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tpt = FA_BM / a.Gc;                              // tokens per CTA
-    // which (entry, first token) is this CTA's?  entries are few: a linear walk
-    int tile = blockIdx.x, e = a.first_entry, q_len = 0;
+    // which (entry, first token) is this CTA's?  entries are few: a linear walk.  The last tiles of a prompt see the most
+    // keys: they start first, so that the short ones fill the device's tail
+    int tile = gridDim.x - 1 - blockIdx.x, e = a.first_entry, q_len = 0;
     for (; e < a.first_entry + a.n_entries; ++e) {
         q_len = a.cu_q[e + 1] - a.cu_q[e];
         const int nt = (q_len + tpt - 1) / tpt;
@@ -435,33 +436,50 @@ fa_decode_kernel(const FaArgs a) {
         sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < a.Gc * a.dv; i += FA_THREADS) {
-        const int row = i / a.dv, dim = i % a.dv;
+    // a row's maximum, its warps' factors and its sum once per row (one thread each); then every thread adds columns
+    float* sF = sL + FA_WARPS * 16;                            // [warp][16] factor of each warp's part, then [16] 1 / sum
+    float* sInv = sF + FA_WARPS * 16;
+    const bool sunk = a.sink != nullptr && a.n_splits == 1;    // keys split over CTAs: the merge adds the sink, once
+    if (threadIdx.x < a.Gc) {
+        const int row = threadIdx.x, head = head0 + row;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
-        const int head = head0 + row;
-        const bool sunk = a.sink != nullptr && a.n_splits == 1;   // keys split over CTAs: the merge adds the sink, once
         const float sk = sunk ? a.sink[head] * 1.4426950408889634f : -INFINITY;
         if (sunk) M = fmaxf(M, sk);
-        float L = 0.0f, O = 0.0f;
-        if (M > -INFINITY) {
+        float L = 0.0f;
 #pragma unroll
-            for (int w = 0; w < FA_WARPS; ++w) {
-                const float f = exp2f(sM[w * 16 + row] - M);   // a warp that saw no key: exp2(-inf) = 0
-                L += sL[w * 16 + row] * f;
-                O += sO[(w * 16 + row) * D + dim] * f;
-            }
-            if (sunk) L += exp2f(sk - M);
+        for (int w = 0; w < FA_WARPS; ++w) {
+            const float f = M > -INFINITY ? exp2f(sM[w * 16 + row] - M) : 0.0f;   // a warp that saw no key: exp2(-inf) = 0
+            sF[w * 16 + row] = f;
+            L += sL[w * 16 + row] * f;
         }
-        float val = L > 0.0f ? O / L * a.out_scale : 0.0f;
-        if (a.n_splits == 1) {
-            if (a.gate) val *= fa_sigmoid(a.gate[(size_t)tok * a.gate_stride + (size_t)head * a.dv + dim]);
-            a.out[((size_t)tok * a.QH + head) * a.dv + dim] = __float2bfloat16_rn(val);
-        } else {
+        if (sunk && M > -INFINITY) L += exp2f(sk - M);
+        sInv[row] = L > 0.0f ? a.out_scale / L : 0.0f;
+        if (a.n_splits > 1) {
             const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
-            a.part_o[pi * a.dv + dim] = val;
-            if (dim == 0) a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
+            a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
+        }
+    }
+    __syncthreads();
+    for (int row = warp; row < a.Gc; row += FA_WARPS) {
+        const int head = head0 + row;
+        const float f0 = sF[row], f1 = sF[16 + row], f2 = sF[32 + row], f3 = sF[48 + row], inv = sInv[row];
+        static_assert(FA_WARPS == 4, "four parts a row");
+        const float* gate = (a.gate && a.n_splits == 1) ? a.gate + (size_t)tok * a.gate_stride + (size_t)head * a.dv : nullptr;
+        const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
+        for (int dim = lane; dim < a.dv; dim += 32) {
+            float O = sO[row * D + dim] * f0;
+            O = fmaf(sO[(16 + row) * D + dim], f1, O);
+            O = fmaf(sO[(32 + row) * D + dim], f2, O);
+            O = fmaf(sO[(48 + row) * D + dim], f3, O);
+            float val = O * inv;
+            if (a.n_splits == 1) {
+                if (gate) val *= fa_sigmoid(gate[dim]);
+                a.out[((size_t)tok * a.QH + head) * a.dv + dim] = __float2bfloat16_rn(val);
+            } else {
+                a.part_o[pi * a.dv + dim] = val;
+            }
         }
     }
 }
@@ -522,7 +540,7 @@ static int fa_launch_prefill(const FaArgs& a, int n_tiles, cudaStream_t s) {
 template <int D, int NST, bool VK>
 static int fa_launch_decode_as(const FaArgs& a, cudaStream_t s) {
     const size_t pipe = (size_t)NST * fa_stage<D, VK>();
-    const size_t merge = (size_t)FA_WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t merge = ((size_t)FA_WARPS * 16 * (D + 3) + 16) * sizeof(float);    // parts, maxima, sums, factors, 1 / sum
     const size_t smem = 16 * FaSmem<D>::STRIDE + (pipe > merge ? pipe : merge);
     static bool done = false;
     if (!done) {

@@ -105,12 +105,16 @@ extern "C" int rb_rotary_heads_append(const void* x, long long x_stride, int x_d
     RB_REFUSE("rotary_heads_append: dtypes %d -> %d", x_dtype, out_dtype);
 }
 
-// One CTA per token.  x row = [a: na | c: nc | r: nr].
+// One CTA per token.  x row = [a: na | c: nc | r: nr].  The row comes into shared memory as floats in one pass (every
+// load in flight at once: with a handful of tokens the kernel is one memory latency, not one per pass); the sums of
+// squares and the outputs read it there.
+#define LP_THREADS 256
 template <typename TX, typename TO>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(LP_THREADS)
 latent_prep_kernel(const TX* __restrict__ x, long long x_stride, int na, int nc, int nr, const float* __restrict__ wa,
                    const float* __restrict__ wc, float eps, const int* __restrict__ positions, const float* __restrict__ freq,
                    int rot, float mag, const int* __restrict__ kv_slot, TO* __restrict__ a_out, TO* __restrict__ cache, int page_size) {
+    extern __shared__ float lp_row[];
     __shared__ float red[32];
     pdl_trigger();
     const int t = blockIdx.x;
@@ -118,28 +122,47 @@ latent_prep_kernel(const TX* __restrict__ x, long long x_stride, int na, int nc,
     const int s = kv_slot ? kv_slot[t] : -1;
     pdl_wait();
     const TX* row = x + (size_t)t * x_stride;
+    const int n = na + nc + nr;
+#pragma unroll 8
+    for (int i = threadIdx.x; i < n; i += LP_THREADS) lp_row[i] = to_f32(row[i]);
+    __syncthreads();
     float sa = 0.0f, sc = 0.0f;
-    for (int i = threadIdx.x; i < na; i += blockDim.x) { const float v = to_f32(row[i]); sa = fmaf(v, v, sa); }
-    for (int i = threadIdx.x; i < nc; i += blockDim.x) { const float v = to_f32(row[na + i]); sc = fmaf(v, v, sc); }
+    for (int i = threadIdx.x; i < na; i += LP_THREADS) { const float v = lp_row[i]; sa = fmaf(v, v, sa); }
+    for (int i = threadIdx.x; i < nc; i += LP_THREADS) { const float v = lp_row[na + i]; sc = fmaf(v, v, sc); }
     sa = block_sum(sa, red);
     sc = block_sum(sc, red);
     const float ia = 1.0f / sqrtf(sa / (float)na + eps), ic = 1.0f / sqrtf(sc / (float)nc + eps);
     TO* ao = a_out + (size_t)t * na;
-    for (int i = threadIdx.x; i < na; i += blockDim.x) ao[i] = from_f32<TO>(to_f32(row[i]) * ia * wa[i]);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < na; i += LP_THREADS) ao[i] = from_f32<TO>(lp_row[i] * ia * wa[i]);
     if (s < 0) return;                                        // an inert row stores nothing
     const int d = nc + nr;
     TO* dst = cache + (size_t)(s / page_size) * page_size * d + (size_t)(s % page_size) * d;
-    for (int i = threadIdx.x; i < nc; i += blockDim.x) dst[i] = from_f32<TO>(to_f32(row[na + i]) * ic * wc[i]);
-    for (int p = threadIdx.x; 2 * p < nr; p += blockDim.x) {
+    for (int i = threadIdx.x; i < nc; i += LP_THREADS) dst[i] = from_f32<TO>(lp_row[na + i] * ic * wc[i]);
+    for (int p = threadIdx.x; 2 * p < nr; p += LP_THREADS) {
         const int i = 2 * p;
-        float u = to_f32(row[na + nc + i]);
+        float u = lp_row[na + nc + i];
         if (i + 1 < nr) {
-            float v = to_f32(row[na + nc + i + 1]);
+            float v = lp_row[na + nc + i + 1];
             if (i + 1 < rot) rh_rotate(u, v, pos, freq[p], mag);
             dst[nc + i + 1] = from_f32<TO>(v);
         }
         dst[nc + i] = from_f32<TO>(u);
     }
+}
+
+template <typename TX, typename TO>
+static int lp_launch(size_t smem, int T, cudaStream_t s, const TX* x, long long x_stride, int na, int nc, int nr, const float* wa,
+                     const float* wc, float eps, const int* positions, const float* freq, int rot, float mag, const int* kv_slot,
+                     TO* a_out, TO* cache, int page_size) {
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(latent_prep_kernel<TX, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed = smem;
+    }
+    return rb_launch(latent_prep_kernel<TX, TO>, dim3(T), dim3(LP_THREADS), smem, s, x, x_stride, na, nc, nr, wa, wc, eps,
+                     positions, freq, rot, mag, kv_slot, a_out, cache, page_size);
 }
 
 // wa [na], wc [nc]: float norm weights (as stored, no offset).  The cache is one layer of a one-head cache whose pages
@@ -152,7 +175,9 @@ extern "C" int rb_latent_prep(const void* x, long long x_stride, int x_dtype, in
     if (rot < 0 || rot % 2 || rot > nr) RB_REFUSE("latent_prep: %d rotated dimensions of %d", rot, nr);
     if (!positions || (rot > 0 && !freq) || !wa || !wc) RB_REFUSE("latent_prep: positions, frequencies and norm weights");
     cudaStream_t s = (cudaStream_t)stream;
-#define LP_GO(TX, TO) return rb_launch(latent_prep_kernel<TX, TO>, dim3(T), dim3(128), 0, s, (const TX*)x, x_stride, na, nc, nr, wa, wc, eps, \
+    const size_t smem = (size_t)(na + nc + nr) * sizeof(float);
+    if (smem > 200 * 1024) RB_REFUSE("latent_prep: a row of %d numbers does not fit shared memory", na + nc + nr);
+#define LP_GO(TX, TO) return lp_launch<TX, TO>(smem, T, s, (const TX*)x, x_stride, na, nc, nr, wa, wc, eps, \
         positions, freq, rot, mag, kv_slot, (TO*)a_out, (TO*)cache, page_size)
     if (x_dtype == RB_F32 && out_dtype == RB_F32) LP_GO(float, float);
     if (x_dtype == RB_F32 && out_dtype == RB_BF16) LP_GO(float, bf16);
