@@ -45,7 +45,15 @@ struct FtArgs {
     // the scaled score; null: none); the last column stands for every greater distance
     const float* bias;
     int bias_last;
+    // decode: a soft cap, score <- cap tanh(score / cap), here cap * log2 e and scale / cap (0: none); a sink per query
+    // head that joins the denominator as exp(sink[h]) without a value, added once (where the splits come together); a
+    // gate, out *= sigmoid(gate[t * gate_stride + h * d + i])
+    float cap_log2, scale_over_cap;
+    const float* sink;
+    const float* gate;
+    long long gate_stride;
 };
+__device__ __forceinline__ float ft_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // With -DRB_TIMELINE a caller may hand the decode kernel a buffer of eight 64-bit words per CTA (linear block index) that
 // get the global timer at: 0 the CTA's start, 1 shared memory zeroed, 2 the kernels before done, 3 the first tile landed,
@@ -115,10 +123,12 @@ __device__ __forceinline__ void ft_merge_park(float* sO, float* sF, const float 
         sF[FT_WARPS * 16 + warp * 16 + row0] = l[0]; sF[FT_WARPS * 16 + warp * 16 + row0 + 8] = l[1];
     }
 }
-__device__ __forceinline__ void ft_merge_weights(float* sF, float* sLse, int Gc) {
+// sink: the row's sink times log2 e where this CTA holds all of the row's keys (-inf: none, or the splits' merge adds it).
+__device__ __forceinline__ void ft_merge_weights(float* sF, float* sLse, int Gc, const float* sink = nullptr, int head0 = 0) {
     const int row = threadIdx.x;
     if (row >= Gc) return;
-    float mw[FT_WARPS], M = -INFINITY, L = 0.0f;
+    const float sk = sink ? sink[head0 + row] * 1.4426950408889634f : -INFINITY;
+    float mw[FT_WARPS], M = sk, L = 0.0f;
 #pragma unroll
     for (int w = 0; w < FT_WARPS; ++w) { mw[w] = sF[w * 16 + row]; M = fmaxf(M, mw[w]); }
 #pragma unroll
@@ -126,6 +136,7 @@ __device__ __forceinline__ void ft_merge_weights(float* sF, float* sLse, int Gc)
         mw[w] = M > -INFINITY ? exp2f(mw[w] - M) : 0.0f;
         L += sF[FT_WARPS * 16 + w * 16 + row] * mw[w];
     }
+    if (sink) L += exp2f(sk - M);
     const float inv = L > 0.0f ? 1.0f / L : 0.0f;
 #pragma unroll
     for (int w = 0; w < FT_WARPS; ++w) sF[w * 16 + row] = mw[w] * inv;
@@ -315,6 +326,11 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int key = k0 + koff + j * 8 + 2 * (lane & 3);
+                if (a.cap_log2 > 0.0f) {                       // the soft cap, in the exponent's base-2 domain, before mask and bias
+                    const float pre = a.cap_log2 / a.scale_log2;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sc[j][c] = pre * tanhf(sc[j][c] * a.scale_over_cap);
+                }
                 sc[j][0] = (key >= lo && key <= pos0) ? sc[j][0] * a.scale_log2 : -INFINITY;
                 sc[j][1] = (key + 1 >= lo && key + 1 <= pos0) ? sc[j][1] * a.scale_log2 : -INFINITY;
                 sc[j][2] = (key >= lo && key <= pos1) ? sc[j][2] * a.scale_log2 : -INFINITY;
@@ -417,7 +433,8 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
             const int row = i / dq, dl = i - row * dq;
             const int dim = split * dq + dl;
             if (dim >= a.d) continue;
-            float M = -INFINITY;
+            const float sk = a.sink ? a.sink[head0 + row] * 1.4426950408889634f : -INFINITY;
+            float M = sk;
             for (int s2 = 0; s2 < a.n_splits; ++s2) M = fmaxf(M, recv_l[s2 * 16 + row]);
             float W = 0.0f, O = 0.0f;
             if (M > -INFINITY) {
@@ -426,8 +443,11 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                     W += w;
                     O += w * recv_o[(s2 * a.Gc + row) * dq + dl];
                 }
+                if (a.sink) W += exp2f(sk - M);
             }
-            a.out[((size_t)tok * a.QH + head0 + row) * a.d + dim] = __float2bfloat16_rn(W > 0.0f ? O / W : 0.0f);
+            float val = W > 0.0f ? O / W : 0.0f;
+            if (a.gate) val *= ft_sigmoid(a.gate[(size_t)tok * a.gate_stride + (size_t)(head0 + row) * a.d + dim]);
+            a.out[((size_t)tok * a.QH + head0 + row) * a.d + dim] = __float2bfloat16_rn(val);
         }
         if (threadIdx.x == 0) FT_T(7);
         return;
@@ -440,7 +460,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
     float* sLse = sF + 2 * FT_WARPS * 16;
     ft_merge_park<D>(sO, sF, o, m, l, a.Gc, warp, lane);
     asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
-    ft_merge_weights(sF, sLse, a.Gc);
+    ft_merge_weights(sF, sLse, a.Gc, a.n_splits == 1 ? a.sink : nullptr, head0);
     asm volatile("bar.sync 1, %0;" ::"n"(FT_WARPS * 32) : "memory");
     for (int dim = threadIdx.x; dim < a.d; dim += FT_WARPS * 32) {
 #pragma unroll 4
@@ -450,6 +470,7 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
             for (int w = 0; w < FT_WARPS; ++w) O += sO[(w * 16 + row) * SD + dim] * sF[w * 16 + row];
             const int head = head0 + row;
             if (a.n_splits == 1) {
+                if (a.gate) O *= ft_sigmoid(a.gate[(size_t)tok * a.gate_stride + (size_t)head * a.d + dim]);
                 a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(O);
             } else {
                 const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
@@ -822,8 +843,9 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
                                 const int* kv_len, void* out, float* part_o, float* part_lse, int first_entry, int n_entries,
                                 int first_tok, int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window,
                                 float scale, const void* next_w, long long next_bytes, const float* bias, int bias_rows,
-                                void* stream) {
+                                float softcap, const float* sink, const float* gate, long long gate_stride, void* stream) {
     if (n_entries <= 0) return 0;
+    if (softcap < 0.0f || (softcap > 0.0f && !(scale > 0.0f))) RB_REFUSE("attention (TMA): a soft cap of %g at scale %g", (double)softcap, (double)scale);
     if (bias && bias_rows <= 0) RB_REFUSE("attention: a distance bias of %d rows", bias_rows);
     if ((uintptr_t)next_w & 15) RB_REFUSE("attention: the range to prefetch must start on a 16-byte boundary");
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
@@ -850,6 +872,10 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     a.next_w = next_w; a.next_bytes = next_bytes;
     a.cluster_merge = cluster_merge ? 1 : 0;
     a.bias = bias; a.bias_last = bias_rows - 1;
+    if (softcap > 0.0f) { a.cap_log2 = softcap * 1.4426950408889634f; a.scale_over_cap = scale / softcap; }
+    a.sink = sink; a.gate = gate; a.gate_stride = gate_stride;
+    if ((sink || gate) && n_splits > 1 && !cluster_merge)
+        RB_REFUSE("attention (TMA): sink and gate are taken where the splits merge inside their cluster (%d splits)", n_splits);
     CUtensorMap map;
     const int box_rows = page_size < FT_BN ? page_size : FT_BN;
     cudaStream_t s = (cudaStream_t)stream;

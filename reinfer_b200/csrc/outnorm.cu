@@ -10,7 +10,9 @@
 template <typename TW, int VEC>
 __global__ void residual_outnorm_kernel(float* __restrict__ x, const float* __restrict__ y, int n_parts, long long part_stride,
                                         const TW* __restrict__ w, bf16* __restrict__ rounded, int h, float eps, float mult,
-                                        const float* __restrict__ extra_a, const void* __restrict__ extra_src, int extra_bf16) {
+                                        const float* __restrict__ extra_a, const void* __restrict__ extra_src, int extra_bf16,
+                                        const float* __restrict__ next_w, bf16* __restrict__ next_rows, float* __restrict__ next_sumsq,
+                                        int next_parts) {
     extern __shared__ __align__(16) float row[];
     __shared__ float red[32];
     pdl_trigger(); pdl_wait();
@@ -52,6 +54,9 @@ __global__ void residual_outnorm_kernel(float* __restrict__ x, const float* __re
     const float f = mult / sqrtf(total / (float)h + eps);
     float* xr = x + (size_t)r * h;
     bf16* rr = rounded ? rounded + (size_t)r * h : nullptr;
+    // the norm that reads the stream next, without its division: rows of x * its weight and the row's sum of squares
+    bf16* nr = next_rows ? next_rows + (size_t)r * h : nullptr;
+    float ss2 = 0.0f;
     if (VEC == 4) {
         for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
             const float4 v = *reinterpret_cast<const float4*>(row + i);
@@ -65,22 +70,42 @@ __global__ void residual_outnorm_kernel(float* __restrict__ x, const float* __re
                 pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
                 *reinterpret_cast<uint2*>(rr + i) = pk;
             }
+            if (nr) {
+                const float4 nw = *reinterpret_cast<const float4*>(next_w + i);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * nw.x, o.y * nw.y), hi = __floats2bfloat162_rn(o.z * nw.z, o.w * nw.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(nr + i) = pk;
+                ss2 += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+            }
         }
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
             const float o = xr[i] + row[i] * f * to_f32(w[i]);
             xr[i] = o;
             if (rr) rr[i] = __float2bfloat16_rn(o);
+            if (nr) { nr[i] = __float2bfloat16_rn(o * next_w[i]); ss2 = fmaf(o, o, ss2); }
         }
+    }
+    if (nr) {
+        const float total2 = block_sum(ss2, red);
+        // (the reader adds a row's parts: the whole sum is the first, the others are zero)
+        for (int p = threadIdx.x; p < next_parts; p += blockDim.x) next_sumsq[(size_t)r * next_parts + p] = p == 0 ? total2 : 0.0f;
     }
 }
 
 // y: n_parts stacked [rows, h] float arrays, part_stride elements apart.  rounded: bfloat16 [rows, h] or null.
-// extra_a [rows] float with extra_src [rows, h] (float or bfloat16), or neither.
+// extra_a [rows] float with extra_src [rows, h] (float or bfloat16), or neither.  next_w [h] float with next_rows
+// [rows, h] bfloat16 and next_sumsq [rows, next_parts] float, or none of them: the rows of the norm that reads the
+// stream next, as rb_residual_rowscale leaves them.
 extern "C" int rb_residual_outnorm(float* x, const float* y, int n_parts, long long part_stride, const void* w, int w_dtype,
                                    void* rounded, int rows, int h, float eps, float mult, const float* extra_a,
-                                   const void* extra_src, int extra_dtype, void* stream) {
+                                   const void* extra_src, int extra_dtype, const float* next_w, void* next_rows,
+                                   float* next_sumsq, int next_parts, void* stream) {
     if (rows <= 0) return 0;
+    if ((next_w == nullptr) != (next_rows == nullptr) || (next_w == nullptr) != (next_sumsq == nullptr) || (next_w && next_parts < 1))
+        RB_REFUSE("outnorm: the next norm's rows need its weight, the rows and the sums");
+    if (next_w && (((uintptr_t)next_w & 15) || ((uintptr_t)next_rows & 7))) RB_REFUSE("outnorm: the next norm's operands must be aligned");
     if ((extra_a == nullptr) != (extra_src == nullptr)) RB_REFUSE("outnorm: half an extra term");
     if (h <= 0 || n_parts < 1) RB_REFUSE("outnorm: width %d, %d partial sums", h, n_parts);
     const size_t smem = (size_t)h * sizeof(float);
@@ -98,7 +123,8 @@ extern "C" int rb_residual_outnorm(float* x, const float* y, int n_parts, long l
             if (e != cudaSuccess) return (int)e; \
         } \
         return rb_launch(residual_outnorm_kernel<TW, V>, dim3(rows), dim3(threads), smem, s, x, y, n_parts, part_stride, \
-                         (const TW*)w, (bf16*)rounded, h, eps, mult, extra_a, extra_src, extra_dtype == RB_BF16 ? 1 : 0); } while (0)
+                         (const TW*)w, (bf16*)rounded, h, eps, mult, extra_a, extra_src, extra_dtype == RB_BF16 ? 1 : 0, \
+                         next_w, (bf16*)next_rows, next_sumsq, next_parts); } while (0)
     if (w_dtype == RB_F32) { if (vec) RB_ON(float, 4); else RB_ON(float, 1); }
     if (w_dtype == RB_BF16) { if (vec) RB_ON(bf16, 4); else RB_ON(bf16, 1); }
 #undef RB_ON

@@ -506,17 +506,24 @@ def decode_cluster_slots(d: int, n: int) -> int:
     return _cluster_slots[key]
 
 
+def decode_merges_in_cluster(n_entries: int, QH: int, KH: int, d: int, n_splits: int) -> bool:
+    """Whether fa_decode_tma's splits would be the CTAs of clusters that merge their results themselves."""
+    ctas = n_entries * KH * (QH // KH // fa_group_chunk(QH // KH)) * n_splits
+    return bool(ATTN_CLUSTER_MERGE and 2 <= n_splits <= min(MAX_CLUSTER_SPLITS, d) and ctas <= CLUSTER_FILL * decode_cluster_slots(d, n_splits))
+
+
 def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-                  bias: Optional[torch.Tensor] = None) -> None:
+                  bias: Optional[torch.Tensor] = None, more: Optional["AttentionExtras"] = None) -> None:
     """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8); bias as in
-    paged_attention_ref.
+    paged_attention_ref; more: soft cap, and - with one split or splits that merge in their cluster - sink and gate.
     Up to 16 splits whose CTAs are all resident at once form clusters that merge their results themselves (no scratch,
     no merge kernel); several waves of CTAs, or more splits, go through scratch and the merge kernel (clusters
     that wait for a free place on one GPC were measured slower there)."""
     part_o = part_lse = None
-    ctas = n_entries * KH * (QH // KH // fa_group_chunk(QH // KH)) * n_splits
-    in_kernel = ATTN_CLUSTER_MERGE and 2 <= n_splits <= min(MAX_CLUSTER_SPLITS, d) and ctas <= CLUSTER_FILL * decode_cluster_slots(d, n_splits)
+    in_kernel = decode_merges_in_cluster(n_entries, QH, KH, d, n_splits)
+    _need(more is None or not more.v_in_k, "fa_decode_tma: the pages hold keys and values")
+    extras = (more or _NO_EXTRAS).flat(QH, d)
     if n_splits > 1 and not in_kernel:
         part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
         part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
@@ -524,7 +531,8 @@ def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     _check(lib().rb_fa_decode_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   _p(part_o), _p(part_lse), c_int(first_entry), c_int(n_entries), c_int(first_tok),
                                   c_int(n_splits), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, *_bias_args(bias, QH), _stream()),
+                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, *_bias_args(bias, QH),
+                                  extras[0], extras[1], extras[3], extras[4], _stream()),
            "fa_decode_tma", *work)
 
 
@@ -1062,10 +1070,12 @@ def chunk_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch
 
 
 def residual_outnorm(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, mult: float,
-                     rounded: Optional[torch.Tensor] = None, extra=None) -> None:
+                     rounded: Optional[torch.Tensor] = None, extra=None, next_w: Optional[torch.Tensor] = None):
     """x (float32 [rows, h]) += mult * rms(y) * w with y float32 [rows, h] or a stack [S, rows, h] of partial sums
     (added in ascending order) and rms(y) = y / sqrt(mean(y^2) + eps); `rounded` (bfloat16 [rows, h]) receives
-    the new x once more, rounded.  extra = (a float32 [rows], src [rows, h]): y[r,:] gets a[r] * src[r,:] added first."""
+    the new x once more, rounded.  extra = (a float32 [rows], src [rows, h]): y[r,:] gets a[r] * src[r,:] added first.
+    next_w (float32 [h], the weight of the norm that reads x next): returns (rows, sumsq) as residual_rowscale does -
+    bfloat16(x * next_w) and the rows' sums of squares [rows, parts] - so that norm costs no launch; else None."""
     _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "outnorm: x float32 [rows, h] contiguous")
     rows, h = x.shape
     _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[-1] == h and y.numel() % max(x.numel(), 1) == 0 and y.numel() >= x.numel(),
@@ -1073,16 +1083,25 @@ def residual_outnorm(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: flo
     _need(rounded is None or (rounded.dtype == torch.bfloat16 and rounded.is_contiguous() and rounded.shape == x.shape),
           "outnorm: the rounded copy is bfloat16 of x's shape")
     if rows == 0:
-        return
+        return None
     ea = es = None
     if extra is not None:
         ea, es = extra
         _need(ea.dtype == torch.float32 and ea.numel() == rows and es.is_contiguous() and tuple(es.shape) == (rows, h),
               "outnorm: the extra term is a float32 factor per row and rows of x's shape")
+    n_rows = n_sumsq = None
+    parts = 0
+    if next_w is not None:
+        _need(next_w.dtype == torch.float32 and next_w.is_contiguous() and next_w.numel() == h, "outnorm: the next norm's weight is float32 [h]")
+        parts = int(lib().rb_rowscale_parts(c_int(h)))
+        n_rows = torch.empty((rows, h), dtype=torch.bfloat16, device=x.device)
+        n_sumsq = torch.empty((rows, parts), dtype=torch.float32, device=x.device)
     _check(lib().rb_residual_outnorm(_p(x), _p(y), c_int(y.numel() // x.numel()), c_longlong(x.numel()), _p(w), c_int(dt(w)),
                                      _p(rounded), c_int(rows), c_int(h), c_float(eps), c_float(mult), _p(ea), _p(es),
-                                     c_int(dt(es) if es is not None else F32), _stream()),
-           "residual_outnorm", 0.0, float((y.numel() + 2 * x.numel()) * 4 + (2 * x.numel() if rounded is not None else 0)))
+                                     c_int(dt(es) if es is not None else F32), _p(next_w), _p(n_rows), _p(n_sumsq), c_int(parts), _stream()),
+           "residual_outnorm", 0.0, float((y.numel() + 2 * x.numel()) * 4 + (2 * x.numel() if rounded is not None else 0) +
+                                          (2 * x.numel() if next_w is not None else 0)))
+    return None if next_w is None else (n_rows, n_sumsq)
 
 
 def round_rows(x: torch.Tensor) -> torch.Tensor:
@@ -1167,8 +1186,8 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
     """Softmax attention of a step's tokens over their requests' pages, causal or in a sliding window, with a
     learned bias by distance (float32 [QH, rows]; a head's last entry serves every greater distance) added to the scaled
     scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv].  more: soft cap, sink, values inside
-    the keys, output gate (AttentionExtras); the decode kernel whose tiles come by TMA does not take them, the tcgen05
-    prefill kernel takes all but values inside the keys."""
+    the keys, output gate (AttentionExtras); the decode kernel whose tiles come by TMA and the tcgen05 prefill kernel take
+    all but values inside the keys."""
     n_dec, E = ctx.n_decode, ctx.n_entries
     dec_work = pre_work = (0.0, 0.0)
     if _profiler is not None:
@@ -1197,10 +1216,13 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
         keys = min(ctx.max_kv_len, window + 63) if window else ctx.max_kv_len
         per = 256 if ctas * -(-keys // 256) >= DECODE_SLOTS // 2 else 128     # few heads and requests: finer splits fill the device
         n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-keys // per), 16))
-        if dk == dv and more is None and tma_pages(group.page_size) and USE_TMA_ATTENTION:
+        tma = dk == dv and (more is None or not more.v_in_k) and tma_pages(group.page_size) and USE_TMA_ATTENTION
+        if tma and more is not None and (more.sink is not None or more.gate is not None) and n_splits > 1:
+            tma = decode_merges_in_cluster(n_dec, QH, KH, dk, n_splits)        # sink and gate enter where the splits come together
+        if tma:
             # key size = value size: the kernel whose tiles come by TMA (up to 16 splits merge inside their cluster)
             fa_decode_tma(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
-                          window, scale, work=dec_work, bias=bias)
+                          window, scale, work=dec_work, bias=bias, more=more)
         else:
             fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
                       window, scale, work=dec_work, dv=dv, bias=bias, more=more)

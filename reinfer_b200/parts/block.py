@@ -60,6 +60,11 @@ def _prepares(norm, reader) -> bool:
     return getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False)
 
 
+def _hands_row_scaled(norm, reader) -> bool:
+    """Whether `norm` may hand rows without their factor to `reader`."""
+    return bool(getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False))
+
+
 def _norm(norm, reader, ctx, x, delta):
     """The norm before `reader`; rows without their factor only where both sides know of them."""
     if getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False):
@@ -175,7 +180,9 @@ class SandwichBlock:
                 raise ValueError("block 'sandwich' needs output norms that add a sublayer's normalised output to the stream (kind 'rms_out')")
 
     @staticmethod
-    def _sublayer(ctx, x, pre, part, post, run, delta=None) -> None:
+    def _sublayer(ctx, x, pre, part, post, run, delta=None, ahead=None):
+        """ahead: the norm that reads the stream after this sublayer, if its reader takes rows without their factor;
+        the output norm's kernel then leaves that norm's rows too (returned, for `delta` of the next sublayer)."""
         xn = _norm(pre, part, ctx, x, delta)
         y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         ctx.fresh_residual, ctx.norm_ahead = True, None
@@ -185,16 +192,23 @@ class SandwichBlock:
                 raise RuntimeError("block 'sandwich': the sublayer did not hand over its output (parts.linear.matmul_into_residual)")
         finally:
             ctx.fresh_residual = False
-        post.add(ctx, x, y if left is None else left, None)
+        return post.add(ctx, x, y if left is None else left, None, ahead=ahead)
+
+    def entry_norm(self):
+        """The norm a block before this one may prepare (rows without their factor, which the mixer takes)."""
+        return self.mixer_norm if _hands_row_scaled(self.mixer_norm, self.mixer) else None
 
     def forward(self, ctx, x, cache, delta=None):
-        if isinstance(delta, PreparedRows):
-            delta = None                            # the product that made them has completed x already
-        self._sublayer(ctx, x, self.mixer_norm, self.mixer, self.mixer_out_norm,
-                       lambda h, y: self.mixer.forward(ctx, h, y, cache), delta)
-        if self.ffn is not None:
-            self._sublayer(ctx, x, self.ffn_norm, self.ffn, self.ffn_out_norm, lambda h, y: self.ffn.forward(ctx, h, y))
-        return None
+        if isinstance(delta, PreparedRows) and delta.norm is not self.mixer_norm:
+            delta = None                            # rows made for another norm; the product that made them has completed x already
+        after = getattr(ctx, "norm_after_block", None)
+        if self.ffn is None:
+            return self._sublayer(ctx, x, self.mixer_norm, self.mixer, self.mixer_out_norm,
+                                  lambda h, y: self.mixer.forward(ctx, h, y, cache), delta, ahead=after)
+        ahead = self.ffn_norm if _hands_row_scaled(self.ffn_norm, self.ffn) else None
+        made = self._sublayer(ctx, x, self.mixer_norm, self.mixer, self.mixer_out_norm,
+                              lambda h, y: self.mixer.forward(ctx, h, y, cache), delta, ahead=ahead)
+        return self._sublayer(ctx, x, self.ffn_norm, self.ffn, self.ffn_out_norm, lambda h, y: self.ffn.forward(ctx, h, y), made, ahead=after)
 
 
 register_part("block", "sandwich", SandwichBlock)

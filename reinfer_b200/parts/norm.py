@@ -87,9 +87,17 @@ class ResidualOutNorm(Norm):
     def bind(self, tensors):
         self.weight = effective_weight(tensors[self.weight_name], self.unit_offset, 1.0)
 
-    def add(self, ctx, x, y, rounded=None, extra=None) -> None:
-        """extra = (a [rows], src [rows, width]): a[r] * src[r] joins y[r] before the norm."""
-        ops.residual_outnorm(x, y, self.weight, self.eps, self.mult, rounded=rounded, extra=extra)
+    def add(self, ctx, x, y, rounded=None, extra=None, ahead=None):
+        """extra = (a [rows], src [rows, width]): a[r] * src[r] joins y[r] before the norm.  ahead: the norm that reads
+        the stream next, for a reader that takes rows without their factor; where its form applies (a decode step's
+        few rows, bfloat16) the same kernel leaves that norm's rows and PreparedRows comes back, else None."""
+        next_w = None
+        if ahead is not None and getattr(ahead, "leaves_row_scale", False) and getattr(ahead, "width", None) == self.width and \
+                ahead.weight is not None and ahead.weight.dtype == torch.float32 and ctx.dtype == torch.bfloat16 and ops.DEFER_SUMS and \
+                0 < x.shape[0] <= ops.STREAMING_TOKENS and self.width % 4 == 0:
+            next_w = ahead.weight
+        made = ops.residual_outnorm(x, y, self.weight, self.eps, self.mult, rounded=rounded, extra=extra, next_w=next_w)
+        return None if made is None else PreparedRows(ahead, made[0], made[1])
 
     def forward(self, ctx, x, out=None, delta=None, row_idx=None):
         raise TypeError("an output norm has no rows to hand on: the block calls add(ctx, x, y)")

@@ -398,3 +398,27 @@ def test_offset_norm_and_output_norm(dtype, h):
     post.add(ctx, stream, y.to(DEV), None)
     want = x.double() + mult * plain.norm_offset(y.double(), w.double(), eps)
     assert (stream.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()              # the stream is 32-bit in every dtype
+
+
+@pytest.mark.parametrize("h", [52, 64, 200, 1030, 2048])
+@pytest.mark.parametrize("stack", [1, 3])
+def test_output_norm_leaves_the_next_norm_its_rows(h, stack):
+    """The output norm's kernel can leave what the norm that reads the stream next needs - the new stream times that
+    norm's weight, and the row's sum of squares - and the stream itself is the same bits with and without."""
+    from reinfer_b200 import ops
+    g = _gen(h + stack)
+    T, eps, mult = 5, 1e-5, 0.4
+    w = torch.randn(h, generator=g).float() * 0.1 + 1.0
+    w_next = torch.randn(h, generator=g).float() * 0.1 + 1.0
+    x = torch.randn(T, h, generator=g) * 3.0
+    y = torch.randn(stack, T, h, generator=g) * 0.3
+    ys = y.double().sum(0)
+    want = x.double() + mult * ys / torch.sqrt((ys * ys).mean(-1, keepdim=True) + eps) * w.double()
+    alone, both = x.to(DEV).clone(), x.to(DEV).clone()
+    assert ops.residual_outnorm(alone, y.to(DEV), w.to(DEV), eps, mult) is None
+    rows, sumsq = ops.residual_outnorm(both, y.to(DEV), w.to(DEV), eps, mult, next_w=w_next.to(DEV))
+    assert torch.equal(alone, both)
+    assert (both.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()
+    assert (rows.double().cpu() - want * w_next.double()).abs().max() <= 1e-2 * want.abs().max()
+    total = sumsq.double().sum(-1).cpu()
+    assert ((total - (want * want).sum(-1)).abs() <= 1e-5 * (want * want).sum(-1)).all()
