@@ -68,6 +68,13 @@ struct FaArgs {
 };
 
 __device__ __forceinline__ float fa_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+// 2^x for x <= 0 or -inf by the special-function unit alone (exp2f wraps range handling around the same instruction;
+// results below 2^-126 are flushed to zero, which P, rounded to bfloat16, and the rescaling factors do not feel)
+__device__ __forceinline__ float fa_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // ---------------------------------------------------------------- small PTX wrappers
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
@@ -210,22 +217,25 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
     const float base0 = mn0 == -INFINITY ? 0.0f : mn0, base1 = mn1 == -INFINITY ? 0.0f : mn1;   // a row that saw no key yet
-    const float c0 = exp2f(m[0] - base0), c1 = exp2f(m[1] - base1);
+    const float c0 = fa_ex2(m[0] - base0), c1 = fa_ex2(m[1] - base1);
     m[0] = mn0; m[1] = mn1;
     float sum0 = 0.0f, sum1 = 0.0f;
     uint32_t p[NT][2];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-        const float e0 = exp2f(s[j][0] - base0), e1 = exp2f(s[j][1] - base0);
-        const float e2 = exp2f(s[j][2] - base1), e3 = exp2f(s[j][3] - base1);
+        const float e0 = fa_ex2(s[j][0] - base0), e1 = fa_ex2(s[j][1] - base0);
+        const float e2 = fa_ex2(s[j][2] - base1), e3 = fa_ex2(s[j][3] - base1);
         sum0 += e0 + e1; sum1 += e2 + e3;
         p[j][0] = pack_bf16(e0, e1);
         p[j][1] = pack_bf16(e2, e3);
     }
     l[0] = l[0] * c0 + sum0;                                   // per-thread partial sums; joined at the end
     l[1] = l[1] * c1 + sum1;
+    // (a tile that raised no row's maximum leaves every factor at one: the whole warp skips the pass over its sums)
+    if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+        for (int j = 0; j < D / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+    }
     // O += P V
 #pragma unroll
     for (int kk = 0; kk < NT / 2; ++kk) {
