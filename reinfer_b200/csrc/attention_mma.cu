@@ -30,7 +30,8 @@
 // stride of their own.  Without them the kernels are what they were.
 //
 // Head sizes: the template is instantiated for 32, 64, 128 and 256; a head size that is a
-// multiple of 8 below the next instance is zero-padded in shared memory.
+// multiple of 8 below the next instance is zero-padded in shared memory.  The prefill kernel has one more shape for a
+// key head of 256 that holds values of at most 192 columns (latent attention): tiles of 32 keys, three CTAs a SM.
 #include "common.cuh"
 
 #define FA_WARPS 4
@@ -104,13 +105,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D> struct FaSmem {
+template <int D, int BN = FA_BN> struct FaSmem {
     static constexpr int STRIDE = D * 2 + 16;                 // bytes per row: 16 bytes of padding keep ldmatrix conflict-free
-    static constexpr int TILE = FA_BN * STRIDE;               // one K or V tile
+    static constexpr int TILE = BN * STRIDE;                  // one K or V tile (BN keys)
     static constexpr int STAGE = 2 * TILE;                    // keys and values
     static constexpr int STAGE_VK = TILE;                     // values inside the keys: the key tile serves both products
 };
-template <int D, bool VK> __host__ __device__ constexpr int fa_stage() { return VK ? FaSmem<D>::STAGE_VK : FaSmem<D>::STAGE; }
+template <int D, bool VK, int BN = FA_BN> __host__ __device__ constexpr int fa_stage() { return VK ? FaSmem<D, BN>::STAGE_VK : FaSmem<D, BN>::STAGE; }
 
 // Copy keys [k0, k0+64) of kv head `kh` (K and V) of the request whose block-table row is `bt`
 // into one stage.  Rows at or beyond `kv_end`, rows in pages that were given back (id < 0) and
@@ -118,11 +119,11 @@ template <int D, bool VK> __host__ __device__ constexpr int fa_stage() { return 
 // A thread always copies the same 16-byte column of rows r0, r0 + RPI, ...; with a page size that
 // is a power of two (page_shift >= 0) the page of a row costs a shift and a mask.  VK: the values are the first dv
 // columns of the key rows and the stage holds the key tile only.
-template <int D, bool VK>
+template <int D, bool VK, int BN = FA_BN>
 __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs& a, const int* bt, int kh, int k0, int kv_end) {
     constexpr int CPR = D / 8;                                // 16-byte chunks per row
     constexpr int RPI = FA_THREADS / CPR;                     // rows per pass over the tile
-    static_assert(FA_THREADS % CPR == 0 && FA_BN % RPI == 0, "tile shape");
+    static_assert(FA_THREADS % CPR == 0 && BN % RPI == 0, "tile shape");
     const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
     const bool kcol_ok = c * 8 < a.d, vcol_ok = c * 8 < a.dv;
     const size_t head_stride = (size_t)a.page_size * a.d, vhead_stride = VK ? head_stride : (size_t)a.page_size * a.dv;
@@ -132,7 +133,7 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
     const bf16* vbase = a.cache + (VK ? 0 : (size_t)a.KH * head_stride) + (size_t)kh * vhead_stride + c * 8;
     unsigned char* dst0 = stage + r0 * FaSmem<D>::STRIDE + c * 16;
 #pragma unroll
-    for (int i = 0; i < FA_BN / RPI; ++i) {
+    for (int i = 0; i < BN / RPI; ++i) {
         const int key = k0 + r0 + i * RPI;
         const bf16* ksrc = a.cache;
         const bf16* vsrc = a.cache;
@@ -149,17 +150,17 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
         }
         unsigned char* dst = dst0 + i * RPI * FaSmem<D>::STRIDE;
         cp_async16(dst, ksrc, kbytes);
-        if (!VK) cp_async16(dst + FaSmem<D>::TILE, vsrc, vbytes);
+        if (!VK) cp_async16(dst + FaSmem<D, BN>::TILE, vsrc, vbytes);
     }
 }
 
 // One 64-key tile for one warp: scores of its 16 rows against NT n-tiles of 8 keys starting at
 // key `koff` of the tile, online softmax, and the P V update.
 //   pos0/pos1, lo0/lo1: last and first visible key of row lane/4 and row lane/4 + 8.
-template <int D, int NT>
+template <int D, int NT, int DO = D>
 __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned char* sK, const unsigned char* sV,
                                         int koff, int k0_abs, int pos0, int pos1, int lo0, int lo1, float scale_log2,
-                                        float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
+                                        float (&o)[DO / 8][4], float (&m)[2], float (&l)[2],
                                         bool pen = false, float pa0 = 0.0f, float pb0 = 0.0f, float pa1 = 0.0f, float pb1 = 0.0f,
                                         const float* bias0 = nullptr, const float* bias1 = nullptr, int bias_stride = 0, int bias_last = 0,
                                         float cap_log2 = 0.0f, float scale_over_cap = 0.0f, int dv_cols = D) {
@@ -234,14 +235,14 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
     // (a tile that raised no row's maximum leaves every factor at one: the whole warp skips the pass over its sums)
     if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {
 #pragma unroll
-        for (int j = 0; j < D / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+        for (int j = 0; j < DO / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
     }
     // O += P V
 #pragma unroll
     for (int kk = 0; kk < NT / 2; ++kk) {
         const uint32_t pa[4] = {p[2 * kk][0], p[2 * kk][1], p[2 * kk + 1][0], p[2 * kk + 1][1]};
 #pragma unroll
-        for (int dp = 0; dp < D / 16; ++dp) {
+        for (int dp = 0; dp < DO / 16; ++dp) {
             if (dp * 16 >= dv_cols) continue;                  // columns beyond the value heads' size stay zero (the same for the whole CTA)
             uint32_t vb[4];
             ldsm_x4_trans(vb, sV + (koff + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + (dp * 16 + 8 * (lane >> 4)) * 2);
@@ -266,11 +267,14 @@ __device__ __forceinline__ void fa_load_q(unsigned char* sQ, const FaArgs& a, in
 }
 
 // ------------------------------------------------------------------------ prefill
-template <int D, bool VK>
-__global__ void __launch_bounds__(FA_THREADS)
+// BN: keys per tile; DO: columns of the sums a warp keeps (>= the value heads' size); MINB: CTAs a SM that the
+// registers are to leave room for.  A key head of 256 that holds its values takes tiles of 32 keys and 192 columns:
+// three CTAs a SM where tiles of 64 keys and 256 columns leave two.
+template <int D, bool VK, int BN = FA_BN, int DO = D, int MINB = 1>
+__global__ void __launch_bounds__(FA_THREADS, MINB)
 fa_prefill_kernel(const FaArgs a) {
     constexpr int NST = 2;
-    constexpr int STAGE = fa_stage<D, VK>();
+    constexpr int STAGE = fa_stage<D, VK, BN>();
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_trigger(); pdl_wait();
     unsigned char* sQ = smem;
@@ -299,7 +303,7 @@ fa_prefill_kernel(const FaArgs a) {
     const int pos_min = start_pos + q0, pos_max = start_pos + q0 + n_tok - 1;
     int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
     if (a.chunk > 0) lo_min = max(lo_min, pos_min / a.chunk * a.chunk);
-    const int t_begin = lo_min / FA_BN, t_end = pos_max / FA_BN + 1;
+    const int t_begin = lo_min / BN, t_end = pos_max / BN + 1;
 
     // this thread's two rows
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
@@ -314,24 +318,24 @@ fa_prefill_kernel(const FaArgs a) {
     const float* bias1 = a.bias ? a.bias + (size_t)hd1 * a.bias_rows : nullptr;
     // keys beyond the last row of this WARP are masked for all its rows: the warp may stop early
     const int warp_last_tok = min(n_tok - 1, (warp * 16 + 15) / a.Gc);
-    const int warp_t_end = (warp * 16) / a.Gc < n_tok ? (start_pos + q0 + warp_last_tok) / FA_BN + 1 : 0;
+    const int warp_t_end = (warp * 16) / a.Gc < n_tok ? (start_pos + q0 + warp_last_tok) / BN + 1 : 0;
 
-    float o[D / 8][4];
+    float o[DO / 8][4];
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+    for (int j = 0; j < DO / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-    fa_load_tile<D, VK>(stages, a, bt, kh, t_begin * FA_BN, kv_end);
+    fa_load_tile<D, VK, BN>(stages, a, bt, kh, t_begin * BN, kv_end);
     cp_async_commit();
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) % NST;
         cp_async_wait<0>();
         __syncthreads();                                       // tile t has landed; tile t-1 is no longer read
-        if (t + 1 < t_end) fa_load_tile<D, VK>(stages + ((buf + 1) % NST) * STAGE, a, bt, kh, (t + 1) * FA_BN, kv_end);
+        if (t + 1 < t_end) fa_load_tile<D, VK, BN>(stages + ((buf + 1) % NST) * STAGE, a, bt, kh, (t + 1) * BN, kv_end);
         cp_async_commit();
         if (t < warp_t_end) {
             const unsigned char* sK = stages + buf * STAGE;
-            fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, VK ? sK : sK + FaSmem<D>::TILE, 0, t * FA_BN,
+            fa_tile<D, BN / 8, DO>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, VK ? sK : sK + FaSmem<D, BN>::TILE, 0, t * BN,
                                   pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
                                   bias0, bias1, 1, a.bias_rows - 1, a.cap_log2, a.scale_over_cap, a.dv);
         }
@@ -356,7 +360,7 @@ fa_prefill_kernel(const FaArgs a) {
     const float* g0 = (a.gate && ti0 < n_tok) ? a.gate + (size_t)(tok_base + ti0) * a.gate_stride + (size_t)hd0 * a.dv : nullptr;
     const float* g1 = (a.gate && ti1 < n_tok) ? a.gate + (size_t)(tok_base + ti1) * a.gate_stride + (size_t)hd1 * a.dv : nullptr;
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
+    for (int j = 0; j < DO / 8; ++j) {
         const int dim = j * 8 + 2 * (lane & 3);
         if (dim >= a.dv) continue;
         if (ti0 < n_tok) {
@@ -532,19 +536,32 @@ static int fa_group_chunk(int G) {                             // largest diviso
     return 1;
 }
 
-template <int D, bool VK>
+template <int D, bool VK, int BN = FA_BN, int DO = D, int MINB = 1>
 static int fa_launch_prefill_as(const FaArgs& a, int n_tiles, cudaStream_t s) {
-    const size_t smem = (size_t)FA_BM * FaSmem<D>::STRIDE + 2 * fa_stage<D, VK>();
+    const size_t smem = (size_t)FA_BM * FaSmem<D>::STRIDE + 2 * fa_stage<D, VK, BN>();
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(fa_prefill_kernel<D, VK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(fa_prefill_kernel<D, VK, BN, DO, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    return rb_launch(fa_prefill_kernel<D, VK>, dim3(n_tiles, a.KH * a.chunks), dim3(FA_THREADS), smem, s, a);
+    return rb_launch(fa_prefill_kernel<D, VK, BN, DO, MINB>, dim3(n_tiles, a.KH * a.chunks), dim3(FA_THREADS), smem, s, a);
 }
 template <int D>
 static int fa_launch_prefill(const FaArgs& a, int n_tiles, cudaStream_t s) {
+    if constexpr (D == 256) {
+        // Tiles of 32 keys and 192 columns of sums put three CTAs on a SM (168 registers, 66 KB) where the plain shape puts
+        // two: more warps to hide the products' latency behind, twice the barriers a key.  It pays once the grid fills the
+        // device several times over (measured: 18 % faster at 7 CTAs a SM, 4 % slower at 3.5).
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        }
+        if (a.v_in_k && a.dv <= 192 && (long long)n_tiles * a.KH * a.chunks >= 6LL * sms)
+            return fa_launch_prefill_as<256, true, 32, 192, 3>(a, n_tiles, s);
+    }
     return a.v_in_k ? fa_launch_prefill_as<D, true>(a, n_tiles, s) : fa_launch_prefill_as<D, false>(a, n_tiles, s);
 }
 template <int D, int NST, bool VK>

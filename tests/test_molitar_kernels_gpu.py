@@ -322,6 +322,43 @@ def test_attention_options_see_what_they_should(dtype, QH, KH, dk, dv, page, sof
         assert (free - ungated).abs().max() > 0.05 * ungated.abs().max()
 
 
+def test_a_long_prompt_over_one_wide_key_head_takes_the_narrow_tiles():
+    """A key head wider than 128 that holds its values (a latent of 104 + 56 rotated, 32 query heads): a prompt long enough
+    that its row tiles fill the device six times over runs on the kernel shape with tiles of 32 keys, a shorter one on
+    tiles of 64.  Both against the plain statement, whole and in two portions, with the first key standing out."""
+    from reinfer_b200 import ops
+    QH, KH, dk, dv, page, dtype = 32, 1, 160, 104, 16, torch.bfloat16
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    row_tiles = -(-6 * sms // (QH // 16))                      # 16 heads a row tile: QH / 16 CTAs per tile of 4 tokens
+    n = 4 * row_tiles + 40
+    g = _gen(n)
+    scale = dk ** -0.5
+    q = torch.randn(n, QH, dk, generator=g)
+    k = torch.randn(n, KH, dk, generator=g)
+    q[:, :, dk - 1] = 2.0
+    k[0, :, dk - 1] = 6.0 / scale                              # a score of 12 above the others' few units
+    q, k = q.to(dtype), k.to(dtype)
+    v = k[:, :, :dv].clone()
+    n_pages = -(-n // page)
+    table = torch.randperm(n_pages + 2, generator=g)[:n_pages].tolist()
+    cache = _paged(k, None, page, KH, dk, dv, n_pages + 2, table).to(DEV)
+    group = SimpleNamespace(block_table=torch.tensor([table], dtype=torch.int32, device=DEV), page_size=page)
+    ref = _plain_attention(q.float(), k.float(), v.float(), scale, None, None, None).double()
+    assert (ref[n - 1, 0] - v[0, 0].double()).abs().max() < 0.05 * v.abs().max()               # the far key takes most of the last row
+
+    def run(lo, hi):
+        more = ops.AttentionExtras(softcap=0.0, sink=None, v_in_k=True, gate=None)
+        out = torch.empty(hi - lo, QH, dv, dtype=dtype, device=DEV)
+        ops.biased_attention(_ctx(lo, hi), q[lo:hi].contiguous().to(DEV), cache, group, out, QH, KH, dk, dv, 0, scale, None, more=more)
+        return out.double().cpu()
+
+    tol = 2e-2 * ref.abs().max()
+    assert (run(0, n) - ref).abs().max() <= tol                                                  # narrow tiles
+    assert (torch.cat([run(0, 37), run(37, n)]) - ref).abs().max() <= tol                       # 37 tokens on tiles of 64, the rest narrow
+    half = n // 2
+    assert (torch.cat([run(0, half), run(half, n)]) - ref).abs().max() <= tol                   # both halves on tiles of 64
+
+
 def test_a_batch_of_unequal_requests_equals_each_alone():
     """Three requests in one launch - two single tokens at different lengths and a portion - against each by itself,
     with cap, sink and gate, and with the values inside one shared key row."""
