@@ -134,7 +134,7 @@ def random_config(seed: int) -> dict:
     mix_kv, mix_vdim = rnd.choice([1, 2, 4]), rnd.choice([8, 16, 20, 64])
     layers = []
     for _ in range(rnd.randint(3, 6)):
-        base = rnd.choice([10.0, 1000.0, 10000.0, 250000.0])
+        base = rnd.choice([10.0, 1000.0, 10000.0, 500000.0])
         if rnd.random() < 0.5:
             dim, rot_dim = rnd.choice([8, 12, 16, 32, 64]), rnd.choice([2, 8, 16, 32])
             dims = rnd.choice([rot_dim, rot_dim, max(2, rot_dim // 2)])

@@ -22,7 +22,7 @@ def _gen(seed):
     return torch.Generator().manual_seed(seed)
 
 
-ROTS = [{"base": 10000.0, "dims": 16}, {"base": 250000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 0.5}},
+ROTS = [{"base": 10000.0, "dims": 16}, {"base": 500000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 0.5}},
         {"base": 50.0, "dims": 8, "scaling": {"factor": 40.0, "original": 16, "fast": 2.0, "slow": 0.25}}, {"base": 7.0, "dims": 2},
         {"base": 100.0, "dims": 12, "scaling": {"factor": 2.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
         {"base": 1000.0, "dims": 24, "scaling": {"factor": 8.0, "original": 32, "fast": 1000.0, "slow": 0.001}}]
