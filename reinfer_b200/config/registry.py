@@ -123,3 +123,5 @@ def _ensure_builtin() -> None:
     _d.register()
     from ..models import molitar as _m
     _m.register()
+    from ..models import zegorax as _z
+    _z.register()

@@ -11,6 +11,7 @@
 // Optionally the kernel also carries a tail along: `tail` columns that follow a head's inputs in x are copied behind
 // the head's outputs in y with their first `rot` dimensions rotated in neighbouring pairs (2i, 2i + 1) by
 // position * freq[i], cosine and sine times `mag` - the rotated part of a query head, which passes the map unchanged.
+// And optionally a gate: float rows [T, H * n_out] (row stride of their own) whose sigmoid multiplies the outputs.
 #include "common.cuh"
 
 #define HG_BM 64
@@ -36,7 +37,8 @@ __device__ __forceinline__ void hg_mma(float (&c)[4], const uint32_t (&a)[4], ui
 __global__ void __launch_bounds__(HG_THREADS)
 heads_linear_mma_kernel(const bf16* __restrict__ x, long long x_row, long long x_head, const bf16* __restrict__ w, bf16* __restrict__ y,
                         long long y_row, long long y_head, int T, int n_in, int n_out, int tail, int rot,
-                        const int* __restrict__ positions, const float* __restrict__ freq, float mag) {
+                        const int* __restrict__ positions, const float* __restrict__ freq, float mag,
+                        const float* __restrict__ gate, long long gate_row) {
     __shared__ __align__(16) unsigned char smem[2 * 2 * HG_TILE];
     pdl_trigger();
     pdl_wait();
@@ -103,7 +105,12 @@ heads_linear_mma_kernel(const bf16* __restrict__ x, long long x_row, long long x
 #pragma unroll
         for (int j = 0; j < HG_BN / 8; ++j) {
             const int o = o0 + j * 8 + 2 * (lane & 3);
-            const float v0 = acc[j][half * 2], v1 = acc[j][half * 2 + 1];
+            float v0 = acc[j][half * 2], v1 = acc[j][half * 2 + 1];
+            if (gate) {                                              // the output gate: times sigmoid(gate[t, h, o])
+                const float* gr = gate + (size_t)t * gate_row + (size_t)h * n_out;
+                if (o < n_out) v0 *= 1.0f / (1.0f + expf(-gr[o]));
+                if (o + 1 < n_out) v1 *= 1.0f / (1.0f + expf(-gr[o + 1]));
+            }
             if (o + 1 < n_out && pairs_ok) *reinterpret_cast<__nv_bfloat162*>(yr + o) = __floats2bfloat162_rn(v0, v1);
             else {
                 if (o < n_out) yr[o] = __float2bfloat16_rn(v0);
@@ -140,7 +147,7 @@ heads_linear_mma_kernel(const bf16* __restrict__ x, long long x_row, long long x
 // multiples of 8 and x 16-byte aligned); w [H, n_out, n_in] contiguous bfloat16, 16-byte aligned; n_in a multiple of 8.
 extern "C" int rb_heads_linear_mma(const void* x, long long x_row, long long x_head, const void* w, void* y, long long y_row,
                                    long long y_head, int T, int H, int n_in, int n_out, int tail, int rot, const int* positions,
-                                   const float* freq, float mag, void* stream) {
+                                   const float* freq, float mag, const float* gate, long long gate_row, void* stream) {
     if (T <= 0 || H <= 0 || n_out <= 0) return 0;
     if (n_in <= 0 || n_in % 8) RB_REFUSE("heads_linear (mma): %d inputs a head (a multiple of 8)", n_in);
     if ((x_row % 8) || (x_head % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
@@ -150,5 +157,5 @@ extern "C" int rb_heads_linear_mma(const void* x, long long x_row, long long x_h
     if (H > 65535 || rb_ceil_div(n_out, HG_BN) > 65535) RB_REFUSE("heads_linear (mma): %d heads, %d outputs", H, n_out);
     return rb_launch(heads_linear_mma_kernel, dim3(rb_ceil_div(T, HG_BM), rb_ceil_div(n_out, HG_BN), H), dim3(HG_THREADS), 0,
                      (cudaStream_t)stream, (const bf16*)x, x_row, x_head, (const bf16*)w, (bf16*)y, y_row, y_head, T, n_in, n_out,
-                     tail, rot, positions, freq, mag);
+                     tail, rot, positions, freq, mag, gate, gate_row);
 }

@@ -3,6 +3,8 @@
 //     chosen, their weights are the scores themselves (not renormalised).  The last outputs may stand for
 //     experts that are the identity.  The result is dense: gates [T, experts] (zero where an expert was not
 //     chosen) and, per token, the sum of the chosen identity experts' scores.
+//     mode 1: the vector added to the router's outputs is a bias of the logits; the `top` largest logits are chosen and
+//     their weights are the softmax over the chosen logits alone.
 //   * the experts' activation with the gate folded in: act[t, e*ff + c] = act(u[t, e*ff + c]) * gates[t, e]
 //     (squared relu), so that ONE product with the experts' down matrices side by side gives the weighted sum of
 //     the chosen experts - an expert that was not chosen contributes exact zeros.
@@ -15,7 +17,41 @@
 // One warp's choice for its token: score [n] holds the router's outputs and becomes the softmax over them; choice [n]
 // is scratch.  Writes the token's row of gates and its identity weight.
 __device__ __forceinline__ void moe_choose(float* score, float* choice, const float* __restrict__ corr, float* __restrict__ gates,
-                                           float* __restrict__ ident, int t, int n, int E, int top, int lane) {
+                                           float* __restrict__ ident, int t, int n, int E, int top, int lane, int mode) {
+    if (mode == 1) {
+        // logits with their bias; the largest are chosen one by one (the first of equal values), then softmaxed alone
+        for (int i = lane; i < n; i += 32) { const float z = score[i] + (corr ? corr[i] : 0.0f); score[i] = z; choice[i] = z; }
+        for (int i = lane; i < E; i += 32) gates[(size_t)t * E + i] = 0.0f;
+        __syncwarp();
+        float zmax = 0.0f, sum = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int i = lane; i < n; i += 32) {
+                const float c = choice[i];
+                if (c > best) { best = c; at = i; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (at >= n) break;
+            if (k == 0) zmax = best;
+            const float e = expf(best - zmax);
+            sum += e;                                            // every lane holds the same values: one order for all
+            if (lane == 0) {
+                choice[at] = -INFINITY;
+                if (at < E) gates[(size_t)t * E + at] = e;
+            }
+            __syncwarp();
+        }
+        const float inv = 1.0f / sum;
+        for (int i = lane; i < E; i += 32) gates[(size_t)t * E + i] *= inv;
+        if (ident && lane == 0) ident[t] = 0.0f;
+        return;
+    }
     float m = -INFINITY;
     for (int i = lane; i < n; i += 32) m = fmaxf(m, score[i]);
     m = warp_max(m);
@@ -58,7 +94,7 @@ __device__ __forceinline__ void moe_choose(float* score, float* choice, const fl
 // z [T, n] float router outputs; corr [n] float (null: none); gates [T, E] float; ident [T] float (null if n == E)
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float* __restrict__ z, const float* __restrict__ corr, float* __restrict__ gates,
-                 float* __restrict__ ident, int T, int n, int E, int top) {
+                 float* __restrict__ ident, int T, int n, int E, int top, int mode) {
     extern __shared__ float sm[];                              // per warp: scores [n], choice [n]
     pdl_trigger(); pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -68,18 +104,18 @@ moe_route_kernel(const float* __restrict__ z, const float* __restrict__ corr, fl
     const float* zr = z + (size_t)t * n;
     for (int i = lane; i < n; i += 32) score[i] = zr[i];
     __syncwarp();
-    moe_choose(score, score + n, corr, gates, ident, t, n, E, top, lane);
+    moe_choose(score, score + n, corr, gates, ident, t, n, E, top, lane, mode);
 }
 
 extern "C" int rb_moe_route(const float* z, const float* corr, float* gates, float* ident, int T, int n, int E, int top,
-                            void* stream) {
+                            int mode, void* stream) {
     if (T <= 0) return 0;
     if (n <= 0 || E < 0 || E > n || top <= 0 || top > n) RB_REFUSE("moe_route: %d outputs, %d experts, top %d", n, E, top);
     if (n > E && !ident) RB_REFUSE("moe_route: identity experts need a place for their weights");
     const size_t smem = (size_t)ROUTE_WARPS * 2 * n * sizeof(float);
     if (smem > 48 * 1024) RB_REFUSE("moe_route: %d router outputs", n);
     return rb_launch(moe_route_kernel, dim3(rb_ceil_div(T, ROUTE_WARPS)), dim3(ROUTE_WARPS * 32), smem, (cudaStream_t)stream,
-                     z, corr, gates, ident, T, n, E, top);
+                     z, corr, gates, ident, T, n, E, top, mode);
 }
 
 // The router's product and its choice in one kernel: z = x W^T in 32-bit, then the same choice.  A CTA takes
@@ -104,7 +140,7 @@ __device__ __forceinline__ void moe_load8(const float* p, float (&v)[8]) {
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 moe_router_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const float* __restrict__ corr, float* __restrict__ gates,
-                  float* __restrict__ ident, int T, int h, int n, int E, int top, int vec) {
+                  float* __restrict__ ident, int T, int h, int n, int E, int top, int vec, int mode) {
     extern __shared__ float sm[];                              // per token: scores [n], choice [n]
     __shared__ float part[ROUTER_THREADS / 32][ROUTER_TOKENS][8];
     pdl_trigger(); pdl_wait();
@@ -169,12 +205,12 @@ moe_router_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const floa
     }
     if (warp < nt) {
         float* score = sm + (size_t)warp * 2 * n;
-        moe_choose(score, score + n, corr, gates, ident, t0 + warp, n, E, top, lane);
+        moe_choose(score, score + n, corr, gates, ident, t0 + warp, n, E, top, lane, mode);
     }
 }
 
 extern "C" int rb_moe_router(const void* x, int x_dtype, const void* w, int w_dtype, const float* corr, float* gates, float* ident,
-                             int T, int h, int n, int E, int top, void* stream) {
+                             int T, int h, int n, int E, int top, int mode, void* stream) {
     if (T <= 0) return 0;
     if (h <= 0 || n <= 0 || E < 0 || E > n || top <= 0 || top > n) RB_REFUSE("moe_router: width %d, %d outputs, %d experts, top %d", h, n, E, top);
     if (n > E && !ident) RB_REFUSE("moe_router: identity experts need a place for their weights");
@@ -184,7 +220,7 @@ extern "C" int rb_moe_router(const void* x, int x_dtype, const void* w, int w_dt
     cudaStream_t s = (cudaStream_t)stream;
     const int vec = h % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0;
     dim3 grid(rb_ceil_div(T, ROUTER_TOKENS)), block(ROUTER_THREADS);
-#define RB_MR(TX, TW) return rb_launch(moe_router_kernel<TX, TW>, grid, block, smem, s, (const TX*)x, (const TW*)w, corr, gates, ident, T, h, n, E, top, vec)
+#define RB_MR(TX, TW) return rb_launch(moe_router_kernel<TX, TW>, grid, block, smem, s, (const TX*)x, (const TW*)w, corr, gates, ident, T, h, n, E, top, vec, mode)
     if (x_dtype == RB_F32 && w_dtype == RB_F32) RB_MR(float, float);
     if (x_dtype == RB_BF16 && w_dtype == RB_BF16) RB_MR(bf16, bf16);
     if (x_dtype == RB_BF16 && w_dtype == RB_F32) RB_MR(bf16, float);

@@ -32,8 +32,9 @@ struct RecurArgs {
     const void* q; long long ldq;          // [T, Hk * dk]   (activation dtype)
     const void* k; long long ldk;          // [T, Hk * dk]
     const void* v; long long ldv;          // [T, H * dv]
-    const float* z; long long ldz;         // [T, H * dk] gate pre-activation without its bias
-    const float* z_bias;                   // [H * dk] or null
+    const float* z; long long ldz;         // [T, H * dk] gate pre-activation without its bias ([T, H] with z_per_head)
+    const float* z_bias;                   // [H * dk] or null ([H] with z_per_head)
+    int z_per_head;                        // one gate per head and token instead of one per key channel
     const void* a_pre; long long lda;      // form 1: removal rate before the sigmoid [T, H * dk] (activation dtype)
     const float* a_bias;                   // form 1: [H * dk] or null
     const void* b_pre; long long ldb;      // form 2: write strength before the sigmoid [T, H]
@@ -96,8 +97,9 @@ __device__ __forceinline__ void recur_prepare(const RecurArgs& A, size_t t, int 
             qv = to_f32(qr[i]) * qn;
             const float kraw = to_f32(kr[i]);
             kv = kraw * kn;
-            float z = A.z[t * A.ldz + (size_t)h * dk + i];
-            if (A.z_bias) z += A.z_bias[(size_t)h * dk + i];
+            const size_t zi = A.z_per_head ? (size_t)h : (size_t)h * dk + i;
+            float z = A.z[t * A.ldz + zi];
+            if (A.z_bias) z += A.z_bias[zi];
             // the gate is kept as g - 1 = expm1(ln g): a gate close to 1 (a memory that lasts thousands of
             // tokens) then keeps the digits of 1 - g that rounding g itself to float would drop
             float lg;
@@ -373,7 +375,7 @@ extern "C" int rb_recurrence_tile(int dk) { return rb_ceil_div(dk, 4) > 32 ? 8 :
 // step's longest portion) exceeds one tile.
 extern "C" int rb_recurrence(int form, int gate, int dtype,
                              const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
-                             const float* z, long long ldz, const float* z_bias,
+                             const float* z, long long ldz, const float* z_bias, int z_per_head,
                              const void* a_pre, long long lda, const float* a_bias,
                              const void* b_pre, long long ldb, const float* rate,
                              float gate_param, float q_scale, int unit_qk,
@@ -388,7 +390,7 @@ extern "C" int rb_recurrence(int form, int gate, int dtype,
     if (gate == 2 && !rate) RB_REFUSE("recurrence: gate 2 needs a rate per head");
     if (n_entries > 65535 || H > 65535) RB_REFUSE("recurrence: %d requests, %d heads exceed the grid", n_entries, H);
     RecurArgs A;
-    A.q = q; A.ldq = ldq; A.k = k; A.ldk = ldk; A.v = v; A.ldv = ldv; A.z = z; A.ldz = ldz; A.z_bias = z_bias;
+    A.q = q; A.ldq = ldq; A.k = k; A.ldk = ldk; A.v = v; A.ldv = ldv; A.z = z; A.ldz = ldz; A.z_bias = z_bias; A.z_per_head = z_per_head;
     A.a_pre = a_pre; A.lda = lda; A.a_bias = a_bias; A.b_pre = b_pre; A.ldb = ldb; A.rate = rate;
     A.gate_param = gate_param; A.q_scale = q_scale; A.unit_qk = unit_qk; A.gate = gate;
     A.state = state; A.out = out; A.cu_q = cu_q; A.entry_slot = entry_slot;

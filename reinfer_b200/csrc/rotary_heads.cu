@@ -10,7 +10,8 @@
 //                             r -> the token's cache slot [c | r] of a one-head cache that holds keys only
 //  * rb_rotate_pairs          a strided block of heads: rotation of the first `rot` of `width` dimensions, the rest copied
 //  * rb_heads_linear          y[t, h, :] = W[h] x[t, h, :] for every head, W [H, out, in]: the plain form (one warp per
-//                             output, ascending sums: a token's result does not depend on the batch)
+//                             output, ascending sums: a token's result does not depend on the batch); optionally
+//                             times the sigmoid of a gate row
 //
 // Angles are float(position) * freq[i] in 32-bit, cosine and sine by sincosf (no fast-math).
 #include "common.cuh"
@@ -32,7 +33,7 @@ rotary_heads_append_kernel(const TX* __restrict__ x, long long x_stride, const f
                            const int* __restrict__ positions, const float* __restrict__ freq, int rot, float mag,
                            const int* __restrict__ kv_slot, TO* __restrict__ q_out, TO* __restrict__ cache,
                            int QH, int KH, int dk, int dv, int page_size, int vmix, const float* __restrict__ lambda,
-                           float* __restrict__ v_first) {
+                           float* __restrict__ v_first, int layout) {
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -52,6 +53,21 @@ rotary_heads_append_kernel(const TX* __restrict__ x, long long x_stride, const f
             const int kh = slot - QH;
             const size_t page_stride = (size_t)KH * page_size * (dk + dv);
             dst = cache + (size_t)(s / page_size) * page_stride + (size_t)kh * page_size * dk + (size_t)(s % page_size) * dk;
+        }
+        if (layout == 1) {                                    // half-split pairing: dimension i turns with i + rot / 2
+            const int half = rot / 2;
+            for (int i = lane; i < dk; i += 32) {
+                if (i < half) {
+                    float u = to_f32(row[col0 + i]) + (bias ? bias[col0 + i] : 0.0f);
+                    float v = to_f32(row[col0 + i + half]) + (bias ? bias[col0 + i + half] : 0.0f);
+                    rh_rotate(u, v, pos, freq[i], mag);
+                    dst[i] = from_f32<TO>(u);
+                    dst[i + half] = from_f32<TO>(v);
+                } else if (i >= rot) {
+                    dst[i] = from_f32<TO>(to_f32(row[col0 + i]) + (bias ? bias[col0 + i] : 0.0f));
+                }
+            }
+            return;
         }
         for (int p = lane; 2 * p < dk; p += 32) {
             const int i = 2 * p;
@@ -82,13 +98,15 @@ rotary_heads_append_kernel(const TX* __restrict__ x, long long x_stride, const f
     }
 }
 
+// layout: 0 neighbouring pairs (2i, 2i + 1); 1 half-split pairs (i, i + rot / 2), both over the first `rot` dimensions.
 // vmix: 0 none; 1 this layer leaves its values (with bias, before rounding) in v_first [T, KH * dv] float; 2 it mixes
 // them in with the weight lambda[0] (a float on the device).
 extern "C" int rb_rotary_heads_append(const void* x, long long x_stride, int x_dtype, const float* bias, const int* positions,
                                       const float* freq, int rot, float mag, const int* kv_slot, void* q_out, void* cache,
                                       int out_dtype, int T, int QH, int KH, int dk, int dv, int page_size, int vmix,
-                                      const float* lambda, float* v_first, void* stream) {
+                                      const float* lambda, float* v_first, int layout, void* stream) {
     if (T <= 0) return 0;
+    if (layout != 0 && layout != 1) RB_REFUSE("rotary_heads_append: pairing %d", layout);
     if (QH <= 0 || KH <= 0 || dk <= 0 || dv <= 0 || page_size <= 0) RB_REFUSE("rotary_heads_append: sizes %d %d %d %d %d", QH, KH, dk, dv, page_size);
     if (rot < 0 || rot % 2 || rot > dk) RB_REFUSE("rotary_heads_append: %d rotated dimensions of %d", rot, dk);
     if (rot > 0 && (!freq || !positions)) RB_REFUSE("rotary_heads_append: a rotation needs frequencies and positions");
@@ -97,7 +115,7 @@ extern "C" int rb_rotary_heads_append(const void* x, long long x_stride, int x_d
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, rb_ceil_div(QH + 2 * KH, RH_WARPS));
 #define RH_GO(TX, TO) return rb_launch(rotary_heads_append_kernel<TX, TO>, grid, dim3(RH_WARPS * 32), 0, s, (const TX*)x, x_stride, bias, \
-        positions, freq, rot, mag, kv_slot, (TO*)q_out, (TO*)cache, QH, KH, dk, dv, page_size, vmix, lambda, v_first)
+        positions, freq, rot, mag, kv_slot, (TO*)q_out, (TO*)cache, QH, KH, dk, dv, page_size, vmix, lambda, v_first, layout)
     if (x_dtype == RB_F32 && out_dtype == RB_F32) RH_GO(float, float);
     if (x_dtype == RB_F32 && out_dtype == RB_BF16) RH_GO(float, bf16);
     if (x_dtype == RB_BF16 && out_dtype == RB_BF16) RH_GO(bf16, bf16);
@@ -230,7 +248,7 @@ extern "C" int rb_rotate_pairs(const void* src, long long src_row, long long src
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(RH_WARPS * 32)
 heads_linear_kernel(const TA* __restrict__ x, long long x_row, long long x_head, const TW* __restrict__ w, TA* __restrict__ y,
-                    long long y_row, long long y_head, int n_in, int n_out) {
+                    long long y_row, long long y_head, int n_in, int n_out, const float* __restrict__ gate, long long gate_row) {
     extern __shared__ float xs[];
     pdl_trigger(); pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -245,20 +263,25 @@ heads_linear_kernel(const TA* __restrict__ x, long long x_row, long long x_head,
         float acc = 0.0f;
         for (int i = lane; i < n_in; i += 32) acc = fmaf(xs[i], to_f32(wr[i]), acc);
         acc = warp_sum(acc);
-        if (lane == 0) yp[o] = from_f32<TA>(acc);
+        if (lane == 0) {
+            if (gate) acc *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_row + (size_t)h * n_out + o]));
+            yp[o] = from_f32<TA>(acc);
+        }
     }
 }
 
 // x [T, H, n_in] and y [T, H, n_out] with row and head strides of their own (in elements); w [H, n_out, n_in] contiguous.
+// gate (null: none): float rows [T, >= H * n_out] with stride gate_row; y is multiplied by sigmoid(gate[t, h * n_out + o]).
 extern "C" int rb_heads_linear(const void* x, long long x_row, long long x_head, int a_dtype, const void* w, int w_dtype, void* y,
-                               long long y_row, long long y_head, int T, int H, int n_in, int n_out, void* stream) {
+                               long long y_row, long long y_head, int T, int H, int n_in, int n_out, const float* gate,
+                               long long gate_row, void* stream) {
     if (T <= 0 || H <= 0 || n_out <= 0) return 0;
     if (n_in <= 0 || n_in > 12288) RB_REFUSE("heads_linear: %d inputs a head (supported: 1..12288)", n_in);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)n_in * sizeof(float);
     dim3 grid(T, H);
 #define HL_GO(TA, TW) return rb_launch(heads_linear_kernel<TA, TW>, grid, dim3(RH_WARPS * 32), smem, s, (const TA*)x, x_row, x_head, (const TW*)w, \
-        (TA*)y, y_row, y_head, n_in, n_out)
+        (TA*)y, y_row, y_head, n_in, n_out, gate, gate_row)
     if (a_dtype == RB_F32 && w_dtype == RB_F32) HL_GO(float, float);
     if (a_dtype == RB_BF16 && w_dtype == RB_BF16) HL_GO(bf16, bf16);
     if (a_dtype == RB_BF16 && w_dtype == RB_F32) HL_GO(bf16, float);

@@ -1133,21 +1133,25 @@ def norm_heads_append(x: torch.Tensor, qw: torch.Tensor, kw: Optional[torch.Tens
                                       _stream()), "norm_heads_append")
 
 
-def moe_route(z: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: int):
+MOE_MODES = {"scores": 0, "chosen_logits": 1}
+
+
+def moe_route(z: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: int, mode: str = "scores"):
     """z float32 [T, n] router outputs -> (gates float32 [T, experts], ident float32 [T] or None): softmax over all n,
     the `top` largest of score + corr chosen, gates = the chosen scores (zero elsewhere), ident = the sum of the chosen
-    scores among the outputs experts..n-1 (experts that are the identity)."""
+    scores among the outputs experts..n-1 (experts that are the identity).  mode "chosen_logits": corr is a bias of the
+    logits, the `top` largest logits are chosen and gates = the softmax over the chosen logits alone."""
     _need(z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2, "moe_route: z float32 [T, n]")
     T, n = z.shape
     _need(corr is None or (corr.dtype == torch.float32 and corr.numel() == n), "moe_route: the correction is float32 [n]")
     gates = torch.empty((T, experts), dtype=torch.float32, device=z.device)
     ident = torch.empty((T,), dtype=torch.float32, device=z.device) if n > experts else None
-    _check(lib().rb_moe_route(_p(z), _p(corr), _p(gates), _p(ident), c_int(T), c_int(n), c_int(experts), c_int(top), _stream()),
-           "moe_route")
+    _check(lib().rb_moe_route(_p(z), _p(corr), _p(gates), _p(ident), c_int(T), c_int(n), c_int(experts), c_int(top), c_int(MOE_MODES[mode]),
+                              _stream()), "moe_route")
     return gates, ident
 
 
-def moe_router(x: torch.Tensor, w: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: int):
+def moe_router(x: torch.Tensor, w: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: int, mode: str = "scores"):
     """The router's product z = x w^T (32-bit, one fixed order per output) and moe_route's choice in one kernel:
     x [T, h], w [n, h] -> (gates float32 [T, experts], ident float32 [T] or None)."""
     _need(x.is_contiguous() and w.is_contiguous() and x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1],
@@ -1157,7 +1161,7 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, corr: Optional[torch.Tensor], e
     gates = torch.empty((T, experts), dtype=torch.float32, device=x.device)
     ident = torch.empty((T,), dtype=torch.float32, device=x.device) if n > experts else None
     _check(lib().rb_moe_router(_p(x), c_int(dt(x)), _p(w), c_int(dt(w)), _p(corr), _p(gates), _p(ident), c_int(T), c_int(x.shape[1]),
-                               c_int(n), c_int(experts), c_int(top), _stream()), "moe_router",
+                               c_int(n), c_int(experts), c_int(top), c_int(MOE_MODES[mode]), _stream()), "moe_router",
            2.0 * T * n * x.shape[1], float(x.numel() * x.element_size() + w.numel() * w.element_size()))
     return gates, ident
 
@@ -1179,6 +1183,44 @@ def rows_axpy(dst: torch.Tensor, a: torch.Tensor, src: torch.Tensor, store: bool
           a.dtype == torch.float32 and a.numel() == dst.shape[0], "rows_axpy: dst float32 [T, h], a float32 [T], src [T, h]")
     _check(lib().rb_rows_axpy(_p(dst), _p(a), _p(src), c_int(dt(src)), c_int(dst.shape[0]), c_int(dst.shape[1]),
                               c_int(int(store)), _stream()), "rows_axpy")
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def glu_act(gu: torch.Tensor, out: torch.Tensor, act: str = "silu", bias: Optional[torch.Tensor] = None,
+            gates: Optional[torch.Tensor] = None, ff: int = 0) -> None:
+    """gu [T, gate: F | up: F] (float32 or the activation dtype; rows may be strided) -> out [T, F]:
+    f(gate + bias) * (up + bias) * gates[t, c // ff].  bias float32 [2F] and gates float32 [T, F // ff] are optional."""
+    T, F_ = out.shape
+    _need(gu.dim() == 2 and gu.stride(1) == 1 and gu.shape == (T, 2 * F_) and out.is_contiguous(), "glu_act: gu [T, 2F], out [T, F]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == 2 * F_), "glu_act: the bias is float32 [2F]")
+    _need(gates is None or (ff > 0 and F_ % ff == 0 and gates.dtype == torch.float32 and gates.is_contiguous() and
+                            tuple(gates.shape) == (T, F_ // ff)), "glu_act: gates float32 [T, F / ff]")
+    _check(lib().rb_glu_act(_p(gu), c_longlong(gu.stride(0)), c_int(dt(gu)), _p(bias), c_int(GLU_ACTS[act]), _p(gates), c_int(ff),
+                            _p(out), c_int(dt(out)), c_int(T), c_int(F_), _stream()), f"glu_act {act}",
+           0.0, float(T * F_ * (2 * gu.element_size() + out.element_size())))
+
+
+def add_row_vector(x: torch.Tensor, b: torch.Tensor) -> None:
+    """x[t, :] += b for every row of the float32 stream."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and b.is_contiguous() and b.numel() == x.shape[1], "add_row_vector: x float32 [T, h], b [h]")
+    _check(lib().rb_add_row_vector(_p(x), _p(b), c_int(dt(b)), c_int(x.shape[0]), c_int(x.shape[1]), _stream()), "add_row_vector")
+
+
+def diff_heads(a: torch.Tensor, out: torch.Tensor, lam: float, eps: float, out_scale: float, H: int, G: int, dv: int,
+               gate: Optional[torch.Tensor] = None) -> None:
+    """The output stage of differential attention: a [T, 2H, dv] holds the two maps' outputs of every head (map m of head
+    g R + r at row (2g + m) R + r, R = H / G); out [T, H, dv] = rms_eps(a1 - lam a2) * out_scale * sigmoid(gate[t, h]).
+    gate: float32 rows [T, H] (rows may be strided) or None."""
+    T = a.shape[0]
+    _need(a.is_contiguous() and out.is_contiguous() and a.dtype == out.dtype and a.numel() == T * 2 * H * dv and
+          out.numel() == T * H * dv, "diff_heads: a [T, 2H, dv], out [T, H, dv], one dtype")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == (T, H)),
+          "diff_heads: the gate is float32 [T, H]")
+    _check(lib().rb_diff_heads(_p(a), c_int(dt(a)), c_float(lam), c_float(eps), c_float(out_scale), _p(gate),
+                               c_longlong(gate.stride(0) if gate is not None else 0), _p(out), c_int(T), c_int(H), c_int(G),
+                               c_int(dv), _stream()), "diff_heads", 0.0, float(3 * T * H * dv * a.element_size()))
 
 
 def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, dk: int, dv: int,
@@ -1242,8 +1284,9 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
 def rotary_heads_append(x: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor, freq: Optional[torch.Tensor],
                         rot: int, mag: float, kv_slot: Optional[torch.Tensor], q_out: torch.Tensor, cache: torch.Tensor,
                         QH: int, KH: int, dk: int, dv: int, page_size: int, vmix: int = 0,
-                        lam: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None) -> None:
+                        lam: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, half_split: bool = False) -> None:
     """x [T, q | k | v | ...] (float32 or bfloat16 rows): + bias (float32 over q | k | v), neighbouring dimensions (2i, 2i+1)
+    (with half_split: dimensions i and i + rot/2)
     of the first `rot` of every q and k head rotated by position * freq[i] with cosine and sine times `mag`, q -> q_out
     [T, QH, dk], k and v into the token's cache slot (pages [K: KH x page x dk | V: KH x page x dv]).  vmix 1: the values
     (with bias) are also left in v_first (float32 [T, KH * dv]); vmix 2: v <- (1 - lam) v + lam v_first first."""
@@ -1256,7 +1299,8 @@ def rotary_heads_append(x: torch.Tensor, bias: Optional[torch.Tensor], positions
     _need(lam is None or (lam.dtype == torch.float32 and lam.numel() == 1), "rotary_heads_append: the mixing weight is one float32 number")
     _check(lib().rb_rotary_heads_append(_p(x), c_longlong(x.stride(0)), c_int(dt(x)), _p(bias), _p(positions), _p(freq), c_int(rot),
                                         c_float(mag), _p(kv_slot), _p(q_out), _p(cache), c_int(dt(q_out)), c_int(x.shape[0]), c_int(QH),
-                                        c_int(KH), c_int(dk), c_int(dv), c_int(page_size), c_int(vmix), _p(lam), _p(v_first), _stream()),
+                                        c_int(KH), c_int(dk), c_int(dv), c_int(page_size), c_int(vmix), _p(lam), _p(v_first), c_int(int(half_split)),
+                                        _stream()),
            "rotary_heads_append", 0.0, float(x.shape[0] * ((QH + KH) * dk + KH * dv) * (x.element_size() + q_out.element_size())))
 
 
@@ -1286,31 +1330,36 @@ def rotate_pairs(src: torch.Tensor, dst: torch.Tensor, positions: torch.Tensor, 
                                  c_int(rot), c_float(mag), _stream()), "rotate_pairs", 0.0, float(2 * src.numel() * src.element_size()))
 
 
-def heads_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, tail=None) -> None:
+def heads_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, tail=None, gate: Optional[torch.Tensor] = None) -> None:
     """y[t, h, :n_out] = w[h] x[t, h, :n_in] for every head: x [T, H, n_in (+ tail)] and y [T, H, n_out (+ tail)] views (last
     dimension contiguous), w [H, n_out, n_in] contiguous.  tail = (positions, freq, rot, mag): the columns of x behind
     the head's inputs go behind the head's outputs in y, their first `rot` dimensions rotated in neighbouring pairs.
     bfloat16: one tensor-core launch for all heads (tail included); else the plain kernel (32-bit sums in ascending order)
-    and `rotate_pairs`.  Either way a token's result does not depend on the batch."""
+    and `rotate_pairs`.  Either way a token's result does not depend on the batch.  gate: float32 rows [T, H * n_out]
+    (rows may be strided) whose sigmoid multiplies the outputs before they are rounded."""
     _need(x.dim() == 3 and y.dim() == 3 and w.dim() == 3 and w.is_contiguous() and x.stride(2) == 1 and y.stride(2) == 1, "heads_linear: views")
     T, H = x.shape[0], x.shape[1]
     n_out, n_in = w.shape[1], w.shape[2]
     n_tail = x.shape[2] - n_in
     _need(w.shape[0] == H and n_tail >= 0 and tuple(y.shape) == (T, H, n_out + n_tail) and x.dtype == y.dtype and
           (n_tail == 0 or tail is not None), "heads_linear: shapes")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == (T, H * n_out)),
+          "heads_linear: the gate is float32 [T, heads * outputs]")
     if T == 0:
         return
+    g_row = c_longlong(gate.stride(0) if gate is not None else 0)
     positions, freq, rot, mag = tail if (tail is not None and n_tail) else (None, None, 0, 1.0)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and n_in % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and \
             x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
         _check(lib().rb_heads_linear_mma(_p(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)), _p(w), _p(y), c_longlong(y.stride(0)),
                                          c_longlong(y.stride(1)), c_int(T), c_int(H), c_int(n_in), c_int(n_out), c_int(n_tail), c_int(rot),
-                                         _p(positions), _p(freq), c_float(mag), _stream()),
+                                         _p(positions), _p(freq), c_float(mag), _p(gate), g_row, _stream()),
                f"heads_linear {n_out}x{n_in}", 2.0 * T * H * n_in * n_out,
                float(H * n_in * n_out * 2 + T * H * (n_in + n_out + 2 * n_tail) * 2))
         return
     _check(lib().rb_heads_linear(_p(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)), c_int(dt(x)), _p(w), c_int(dt(w)), _p(y),
-                                 c_longlong(y.stride(0)), c_longlong(y.stride(1)), c_int(T), c_int(H), c_int(n_in), c_int(n_out), _stream()),
+                                 c_longlong(y.stride(0)), c_longlong(y.stride(1)), c_int(T), c_int(H), c_int(n_in), c_int(n_out), _p(gate), g_row,
+                                 _stream()),
            f"heads_linear {n_out}x{n_in}", 2.0 * T * H * n_in * n_out,
            float(H * n_in * n_out * w.element_size() + T * H * (n_in + n_out) * x.element_size()))
     if n_tail:
@@ -1326,11 +1375,11 @@ def recurrence(form: str, gate: str, q: torch.Tensor, k: torch.Tensor, v: torch.
                entry_slot: torch.Tensor, n_entries: int, H: int, Hk: int, dk: int, dv: int, *, gate_param: float = 0.0,
                q_scale: float = 1.0, unit_qk: bool = False, a_pre: Optional[torch.Tensor] = None,
                a_bias: Optional[torch.Tensor] = None, b_pre: Optional[torch.Tensor] = None,
-               rate: Optional[torch.Tensor] = None, max_q_len: int = 1 << 30) -> None:
+               rate: Optional[torch.Tensor] = None, max_q_len: int = 1 << 30, gate_per_head: bool = False) -> None:
     """The token-by-token recurrence over state [slots, H, dk, dv] (float32) of csrc/recurrence.cu.  q, k [T, Hk*dk],
     v [T, H*dv], a_pre [T, H*dk], b_pre [T, H] in the activation dtype (rows may be strided); z [T, H*dk] float32;
     z_bias, a_bias [H*dk] and rate [H] float32; out [T, H, dv] float32.  max_q_len: the step's longest portion (the
-    default says "unknown: may be long")."""
+    default says "unknown: may be long").  gate_per_head: one gate per head and token, z [T, H] and z_bias [H]."""
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv),
           "recurrence: state float32 [slots, H, dk, dv]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and z.dtype == torch.float32, "recurrence: out and z float32")
@@ -1348,7 +1397,7 @@ def recurrence(form: str, gate: str, q: torch.Tensor, k: torch.Tensor, v: torch.
         prep = torch.empty(T * H * int(lib().rb_recurrence_record_floats(c_int(RECURRENCE_FORMS[form]), c_int(dk), c_int(dv))),
                            dtype=torch.float32, device=q.device)
     _check(lib().rb_recurrence(c_int(RECURRENCE_FORMS[form]), c_int(RECURRENCE_GATES[gate]), c_int(dt(q)),
-                               _p(q), ld(q), _p(k), ld(k), _p(v), ld(v), _p(z), ld(z), _p(z_bias),
+                               _p(q), ld(q), _p(k), ld(k), _p(v), ld(v), _p(z), ld(z), _p(z_bias), c_int(int(gate_per_head)),
                                _p(a_pre), ld(a_pre), _p(a_bias), _p(b_pre), ld(b_pre), _p(rate),
                                c_float(gate_param), c_float(q_scale), c_int(int(unit_qk)),
                                _p(state), _p(out), _p(cu_q), _p(entry_slot), c_int(n_entries), c_int(H), c_int(Hk),

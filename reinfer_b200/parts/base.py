@@ -196,3 +196,4 @@ def _ensure_builtin() -> None:
     from . import dyt, chunk_attention, linear_recurrence, parallel  # noqa: F401
     from . import biased_attention, moe  # noqa: F401
     from . import latent_attention, gated_attention  # noqa: F401
+    from . import diff_attention  # noqa: F401

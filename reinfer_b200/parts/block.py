@@ -211,6 +211,47 @@ class SandwichBlock:
         return self._sublayer(ctx, x, self.ffn_norm, self.ffn, self.ffn_out_norm, lambda h, y: self.ffn.forward(ctx, h, y), made, ahead=after)
 
 
+class ParallelBlock:
+    """h = norm(x);  x += mixer(h) + ffn(h): ONE norm, and both sublayers read its rows.  The feed-forward is optional.
+    The mixer adds into the stream itself (nothing of it may be left to a later norm: the feed-forward's last product
+    has to see the stream with the mixer's share in it, where it does the next norm's work); what the feed-forward
+    leaves is the block's own result."""
+    roles = ("mixer_norm", "mixer")
+    hands_on_sums = True
+
+    def __init__(self, parts):
+        need_roles("parallel", parts, self.roles)
+        self.norm, self.mixer, self.ffn = parts["mixer_norm"], parts["mixer"], parts.get("ffn")
+
+    def forward(self, ctx, x, cache, delta=None):
+        h = self.norm.forward(ctx, x, delta=delta)
+        after = getattr(ctx, "norm_after_block", None)
+        if self.ffn is None:
+            ctx.norm_ahead = after
+            try:
+                return self.mixer.forward(ctx, h, x, cache)
+            finally:
+                ctx.norm_ahead = None
+        defer = ctx.defer_residual
+        ctx.defer_residual, ctx.norm_ahead = False, None
+        try:
+            left = self.mixer.forward(ctx, h, x, cache)
+        finally:
+            ctx.defer_residual = defer
+        if left is not None:                        # a mixer that hands its sum on all the same
+            for part in (left if left.dim() == 3 else left.unsqueeze(0)):
+                ops.residual_add(x, part.contiguous())
+        ctx.norm_ahead = after
+        try:
+            return self.ffn.forward(ctx, h, x)
+        finally:
+            ctx.norm_ahead = None
+
+    def entry_norm(self):
+        return self.norm if getattr(self.norm, "prepares_complete_rows", False) and hasattr(self.norm, "prepared_by") else None
+
+
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "out_norm", OutNormBlock)

@@ -14,6 +14,10 @@
                  g = exp(-exp(A_log[h]) softplus(W_a2 W_a1 h + dt_bias)),  beta = sigmoid(W_b h);
                  o per head over its root mean square, times a shared weight, times sigmoid(W_g2 W_g1 h).
 
+  head_delta     the gated delta rule with ONE decay per head and token: as channel_delta, but
+                 g = exp(-exp(A_log[h]) softplus(W_a h + dt_bias[h])) is a scalar of the head, and the read-out
+                 is gated by silu(W_g h) (full rank).
+
 Every input projection of a mixer is one product with the rows of its matrices concatenated at load
 (padded to a multiple of 8 rows so that slices of the result can feed the next product); gates,
 decays, unit vectors and the state are float32 in both precisions.  All read the step's entries from
@@ -181,6 +185,48 @@ class ChannelGatedDeltaRule(_RecurrentMixer):
         return matmul_into_residual(ctx, out, self.w_o, residual)
 
 
+class HeadGatedDeltaRule(_RecurrentMixer):
+    def __init__(self, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, conv: int, eps: float, out_scale: float = 1.0):
+        self.hidden, self.H, self.G, self.dk, self.dv = int(hidden), int(heads), int(kv_heads), int(dim), int(vdim)
+        if self.G <= 0 or self.H % self.G:
+            raise ValueError(f"head_delta: {self.H} heads over {self.G} key heads")
+        self.eps, self.out_scale = float(eps), float(out_scale)
+        self.conv = ShortConv(("q.conv", "k.conv", "v.conv"), (self.G * self.dk, self.G * self.dk, self.H * self.dv), conv)
+
+    def param_specs(self):
+        h, H, G, dk, dv = self.hidden, self.H, self.G, self.dk, self.dv
+        out = {"q": ParamSpec((G * dk, h)), "k": ParamSpec((G * dk, h)), "v": ParamSpec((H * dv, h)),
+               "a": ParamSpec((H, h), std=0.1), "b": ParamSpec((H, h)), "g": ParamSpec((H * dv, h)),
+               "A_log": ParamSpec((H,), std=0.5), "dt_bias": ParamSpec((H,), std=1.0),
+               "norm": ParamSpec((dv,), init="norm"), "o": ParamSpec((h, H * dv))}
+        out.update(self.conv.param_specs())
+        return out
+
+    def state_spec(self):
+        return {"S": SlotStateSpec((self.H, self.dk, self.dv), "float32"), "conv": self.conv.state_spec()}
+
+    def bind(self, t):
+        self._fuse(t, ["q", "k", "v", "g", "b"])
+        self.conv.bind(t)
+        self.w_a, self.w_o = t["a"], t["o"]
+        self.dt_bias, self.a_log, self.norm_w = _f32(t["dt_bias"]), _f32(t["A_log"]), _f32(t["norm"])
+
+    def forward(self, ctx, xn, residual, cache):
+        T, H, G, dk, dv = xn.shape[0], self.H, self.G, self.dk, self.dv
+        proj = matmul(ctx, xn, self.w_in)
+        z = matmul(ctx, xn, self.w_a, out_dtype=torch.float32)              # the decay's pre-activation, one a head: 32-bit sums
+        y = self.conv.forward(ctx, self._col(proj, "q", upto="v"), cache.state["conv"], silu=True)
+        o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
+        ops.recurrence("delta_gated_state", "exp_softplus", y[:, :G * dk], y[:, G * dk:2 * G * dk], y[:, 2 * G * dk:],
+                       z, self.dt_bias, cache.state["S"], o, ctx.cu_q, ctx.entry_slot, ctx.n_entries, H, G, dk, dv,
+                       q_scale=dk ** -0.5, unit_qk=True, b_pre=self._col(proj, "b"), rate=self.a_log, max_q_len=ctx.max_q_len,
+                       gate_per_head=True)
+        out = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
+        ops.head_norm_gate(o, self.norm_w, self._col(proj, "g"), out, H, dv, self.eps, "silu", self.out_scale)
+        return matmul_into_residual(ctx, out, self.w_o, residual)
+
+
+register_part("mixer", "head_delta", HeadGatedDeltaRule)
 register_part("mixer", "gla", GatedLinearAttention)
 register_part("mixer", "general_delta", GeneralDeltaRule)
 register_part("mixer", "channel_delta", ChannelGatedDeltaRule)

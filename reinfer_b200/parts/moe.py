@@ -7,6 +7,11 @@
 An expert is down(act(up(x))) with act = relu(.)^2 and no biases; the last `identity` choices are experts that
 hand their input back unchanged and have no tensors.
 
+Two options make the other common form.  `gated=True`: an expert is down(f(gate(x)) * up(x)) with f = `activation`
+(silu or the tanh form of gelu), three tensors an expert.  `route="chosen_logits"`: the vector beside the router's matrix
+(`correction_name`) is a bias of the logits, the `top` largest logits are chosen and the weights are the softmax over the
+chosen logits alone.
+
 The experts' up matrices are stacked by rows at load and their down matrices side by side, and the router's choice
 is kept dense (gates [T, experts], zero where an expert was not chosen): one product makes every expert's inner
 activations, the activation kernel multiplies each by its token's gate, and one product with the stacked down
@@ -25,11 +30,19 @@ from .linear import matmul, matmul_into_residual
 
 class ExpertMixture(FeedForward):
     def __init__(self, hidden: int, experts: int, top: int, inner: int, identity: int = 0,
-                 expert_names=("e{}.up", "e{}.down"), router_name: str = "router", correction_name: str = "correction"):
+                 expert_names=("e{}.up", "e{}.down"), router_name: str = "router", correction_name: str = "correction",
+                 gated: bool = False, activation: str = "silu", route: str = "scores"):
+        """expert_names: (up, down), or with `gated` (gate, up, down) - patterns that take the expert's index."""
         self.hidden, self.E, self.I, self.top, self.ff = int(hidden), int(experts), int(identity), int(top), int(inner)
         if self.E < 1 or self.I < 0 or not 1 <= self.top <= self.E + self.I:
             raise ValueError(f"expert mixture: {self.E} experts, {self.I} identity experts, top {self.top}")
-        self.up_name, self.down_name = expert_names
+        self.gated, self.activation, self.route = bool(gated), activation, route
+        if route not in ops.MOE_MODES or (self.gated and activation not in ops.GLU_ACTS):
+            raise ValueError(f"expert mixture: route {route!r}, activation {activation!r}")
+        if len(expert_names) != (3 if self.gated else 2):
+            raise ValueError("expert mixture: tensor names for (gate,) up and down")
+        self.gate_name = expert_names[0] if self.gated else None
+        self.up_name, self.down_name = expert_names[-2:]
         self.router_name, self.correction_name = router_name, correction_name
         self.w_up = self.w_down = self.w_router = self.correction = None
 
@@ -37,24 +50,33 @@ class ExpertMixture(FeedForward):
         h, n = self.hidden, self.E + self.I
         out = {self.router_name: ParamSpec((n, h), std=0.1), self.correction_name: ParamSpec((n,), std=0.02)}
         for e in range(self.E):
+            if self.gated:
+                out[self.gate_name.format(e)] = ParamSpec((self.ff, h))
             out[self.up_name.format(e)] = ParamSpec((self.ff, h))
             out[self.down_name.format(e)] = ParamSpec((h, self.ff))
         return out
 
     def bind(self, t):
         ups = [t[self.up_name.format(e)] for e in range(self.E)]
+        if self.gated:
+            ups = [t[self.gate_name.format(e)] for e in range(self.E)] + ups     # [all gates; all ups]: one gated pair over E * ff columns
         downs = [t[self.down_name.format(e)] for e in range(self.E)]
         if len({m.dtype for m in ups + downs}) > 1:
             ups, downs = [m.float() for m in ups], [m.float() for m in downs]
-        self.w_up = torch.cat(ups, dim=0).contiguous()                  # [E * ff, h]
+        self.w_up = torch.cat(ups, dim=0).contiguous()                  # [E * ff, h]  (gated: [2 * E * ff, h])
         self.w_down = torch.cat(downs, dim=1).contiguous()              # [h, E * ff]
         self.w_router = t[self.router_name]
         self.correction = t[self.correction_name].float().contiguous()
 
     def forward(self, ctx, xn, residual):
         T = xn.shape[0]
-        gates, ident = ops.moe_router(xn, self.w_router, self.correction, self.E, self.top)     # 32-bit, product and choice
-        act = ops.relu2_gate(matmul(ctx, xn, self.w_up), gates, self.ff)
+        gates, ident = ops.moe_router(xn, self.w_router, self.correction, self.E, self.top, mode=self.route)     # 32-bit, product and choice
+        if self.gated:
+            act = torch.empty((T, self.E * self.ff), dtype=xn.dtype, device=xn.device)
+            if T:
+                ops.glu_act(matmul(ctx, xn, self.w_up, out_dtype=torch.float32), act, self.activation, None, gates, self.ff)
+        else:
+            act = ops.relu2_gate(matmul(ctx, xn, self.w_up), gates, self.ff)
         if ident is not None:
             ctx.norm_ahead = None           # the stream is not complete behind the down product: nobody's rows can be made there
         left = matmul_into_residual(ctx, act, self.w_down, residual)

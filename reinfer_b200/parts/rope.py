@@ -17,17 +17,35 @@ from .base import PositionEncoding, register_part
 
 
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int = 0):
+    """`scaling` = {factor, low, high, original} stretches the slow pairs by wavelength: with l = 2 pi / f, a frequency
+    with l < original / high stays, one with l > original / low becomes f / factor, and between the two it is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = 0, scaling: Optional[dict] = None):
         self.head_dim = int(head_dim)
         self.theta = float(theta)
         self.rotary_dim = int(rotary_dim) or self.head_dim
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary width {self.rotary_dim} of head_dim {self.head_dim}")
+        self.scaling = None
+        if scaling:
+            self.scaling = {k: float(scaling[k]) for k in ("factor", "low", "high", "original")}
+            if min(self.scaling.values()) <= 0 or self.scaling["high"] == self.scaling["low"]:
+                raise ValueError(f"rotation: scaling {scaling}")
         self.inv_freq = None
 
     def table(self) -> torch.Tensor:
-        p = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-        return (torch.tensor(self.theta, dtype=torch.float64) ** (-(2.0 * p) / self.rotary_dim)).to(torch.float32)
+        f = [self.theta ** (-2.0 * p / self.rotary_dim) for p in range(self.rotary_dim // 2)]
+        sc = self.scaling
+        if sc:
+            for p, fp in enumerate(f):
+                wave = 2.0 * math.pi / fp
+                if wave > sc["original"] / sc["low"]:
+                    f[p] = fp / sc["factor"]
+                elif wave >= sc["original"] / sc["high"]:
+                    s = (sc["original"] / wave - sc["low"]) / (sc["high"] - sc["low"])
+                    f[p] = (1.0 - s) * fp / sc["factor"] + s * fp
+        return torch.tensor(f, dtype=torch.float64).to(torch.float32)
 
     def prepare(self, device) -> None:
         self.inv_freq = self.table().to(device)
@@ -36,7 +54,8 @@ class RotaryEncoding(PositionEncoding):
         return self.inv_freq, self.rotary_dim
 
     def table_key(self):
-        return ("rope", self.theta, self.rotary_dim)
+        sc = tuple(sorted(self.scaling.items())) if self.scaling else None
+        return ("rope", self.theta, self.rotary_dim, sc)
 
     def apply(self, ctx, q, k, positions) -> None:
         """The unfused form, for a mixer that does not take `fused_rotary()`: q [T, QH, d] and k [T, KH, d]
