@@ -85,7 +85,7 @@ DESIGN_SIZES = {"w2048": dict(width=2048, heads=16, ff=8192, layers=6), "w4096":
 
 
 def design_run(a, measure) -> int:
-    """--design silutar|damadra|molitar: that design and the closest existing one (Qwen3) at equal layer sizes, bf16 random weights:
+    """--design silutar|damadra|molitar|zegorax: that design and the closest existing one (Qwen3) at equal layer sizes, bf16 random weights:
     prefill of 2,048 tokens and decode at --batch requests of 2,048 tokens, device time by CUDA events, and one eager
     step of each kind by kernel family with each family's share of the measured peaks."""
     hbm_gbs, tf_burst, _, peak_src = measure.peaks(ROOT)
@@ -94,7 +94,8 @@ def design_run(a, measure) -> int:
     sizes = {}
     for name, sz in DESIGN_SIZES.items():
         row = {}
-        for design, make in ((a.design, {"silutar": measure.silutar_shape, "damadra": measure.damadra_shape, "molitar": measure.molitar_shape}[a.design]),
+        for design, make in ((a.design, {"silutar": measure.silutar_shape, "damadra": measure.damadra_shape, "molitar": measure.molitar_shape,
+                                                "zegorax": measure.zegorax_shape}[a.design]),
                              ("qwen3", measure.qwen3_shape)):
             r = measure.time_design(make(**sz), prompt=2048, batch=a.batch, context=2048, steps=max(8, a.steps // 2),
                                     page_size=a.page_size, segments=not a.no_segments)
@@ -128,7 +129,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--no-segments", action="store_true")
-    ap.add_argument("--design", default=None, choices=["silutar", "damadra", "molitar"],
+    ap.add_argument("--design", default=None, choices=["silutar", "damadra", "molitar", "zegorax"],
                     help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
                          "Qwen3 at equal sizes (random weights); prints one JSON line of its own")
     a = ap.parse_args()

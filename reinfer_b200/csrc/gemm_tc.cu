@@ -73,6 +73,24 @@ struct TcShared {                        // after the operand stages, in dynamic
     float row_scale[256];                // the factor that each token's results are multiplied by (1 if none)
 };
 
+// What the gated pair's epilogue does beside silu(gate) * up (all optional; zeros: nothing): a bias on the gate and on the
+// up features (float [2F]: gate biases, then up biases), the tanh form of gelu in the place of silu (kind 1), and a factor
+// per token and block of `ff` features (float [T, n_exp]: the weight of an expert of a mixture whose experts' pairs were
+// stacked; zero where the expert was not chosen).
+struct TcGlu {
+    const float* bias;
+    const float* gates;
+    int kind, ff, n_exp, F;
+};
+
+__device__ __forceinline__ float tc_glu(const TcGlu& gl, float g, float u, int feat, int tok) {
+    if (gl.bias) { g += gl.bias[feat]; u += gl.bias[gl.F + feat]; }
+    const float a = gl.kind == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+    float v = a * u;
+    if (gl.gates) v *= gl.gates[(size_t)tok * gl.n_exp + feat / gl.ff];
+    return v;
+}
+
 // What a product over one token tile may be told beside its operands.
 struct TcExtra {
     // A range that the CTAs call into L2 once their own weights have arrived (null: none).
@@ -111,6 +129,7 @@ struct TcExtra {
     const void* h_k_w;
     int h_w_f32, h_QH, h_KH, h_page;
     float h_eps;
+    TcGlu glu;                           // the gated pair's epilogue (DUAL)
 };
 
 // Cosines, sines and norm weights of the four features f4 .. f4 + 3 of a query or key head for token t (heads in the
@@ -304,7 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const float g = __uint_as_float(r[j]), u = __uint_as_float(r2[j]);
-                            if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                            if (j < nt) cp[(size_t)j * ldc] = __float2bfloat16_rn(tc_glu(ex.glu, g, u, feat, t0 + c0 + j));
                         }
                     } else if (out_mode == 2) {
                         // read-modify-write of the float residual: all loads first, so that their
@@ -509,7 +528,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (DUAL) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * (u[i] * f);
+                    for (int i = 0; i < 4; ++i) v[i] = tc_glu(ex.glu, v[i], u[i] * f, min(feat + i, N - 1), t0 + cb);
                 }
                 const size_t at = (size_t)(t0 + cb) * ldc + feat;
 #pragma unroll
@@ -574,6 +593,7 @@ struct TcRows {
     const float* row_sumsq;
     int sumsq_parts;
     float inv_width, eps;
+    TcGlu glu;                           // the gated pair's epilogue (MODE 1)
 };
 
 template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
@@ -765,7 +785,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                         for (int j = 0; j < 8; ++j) {
                             const float g0 = __uint_as_float(r[2 * j]) * rf, u0 = __uint_as_float(r2[2 * j]) * rf;
                             const float g1 = __uint_as_float(r[2 * j + 1]) * rf, u1 = __uint_as_float(r2[2 * j + 1]) * rf;
-                            const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                            const int f0 = min(n0 + c0 + 2 * j, N - 1), f1 = min(n0 + c0 + 2 * j + 1, N - 1);
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(tc_glu(rs.glu, g0, u0, f0, tok), tc_glu(rs.glu, g1, u1, f1, tok));
                             o[j] = *(const uint32_t*)&v;
                         }
                         if (vec_ok && n0 + c0 + 16 <= N) {
@@ -1117,7 +1138,8 @@ gemm_tc_gated_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __g
                 for (int j = 0; j < 8; ++j) {
                     const float g0 = __uint_as_float(r[2 * j]) * f, u0 = __uint_as_float(r2[2 * j]) * f;
                     const float g1 = __uint_as_float(r[2 * j + 1]) * f, u1 = __uint_as_float(r2[2 * j + 1]) * f;
-                    const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                    const int f0 = min(n0 + c0 + 2 * j, F - 1), f1 = min(n0 + c0 + 2 * j + 1, F - 1);
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(tc_glu(ex.glu, g0, u0, f0, tok), tc_glu(ex.glu, g1, u1, f1, tok));
                     o[j] = *(const uint32_t*)&v;
                 }
                 if (vec_ok && n0 + c0 + 16 <= F) {
@@ -1358,6 +1380,7 @@ static int tc_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T 
 static TcRows tc_rows(const TcExtra& ex) {
     TcRows rs{};
     rs.row_sumsq = ex.row_sumsq; rs.sumsq_parts = ex.sumsq_parts; rs.inv_width = ex.inv_width; rs.eps = ex.eps;
+    rs.glu = ex.glu;
     return rs;
 }
 
@@ -1392,6 +1415,7 @@ static int tc_extra(TcExtra* ex, const void* next_w, long long next_bytes, const
     ex->prep_w = nullptr; ex->prep_w_f32 = 0; ex->prep_rows = nullptr; ex->prep_sumsq = nullptr; ex->prep_b = nullptr; ex->prep_alpha = nullptr;
     ex->h_q_out = nullptr; ex->h_cache = nullptr; ex->h_kv_slot = nullptr; ex->h_positions = nullptr; ex->h_inv_freq = nullptr;
     ex->h_q_w = ex->h_k_w = nullptr; ex->h_w_f32 = 0; ex->h_QH = ex->h_KH = 0; ex->h_page = 1; ex->h_eps = 0.0f;
+    ex->glu = TcGlu{nullptr, nullptr, 0, 1, 1, 0};
     return 0;
 }
 
@@ -1642,15 +1666,22 @@ extern "C" int rb_gemm_qkv_heads(const void* X, const void* W, int T, int K, lon
 
 // act[T,F] (bfloat16) = silu(X Wg^T) * (X Wu^T) for Wgu = [Wg; Wu] of shape [2F, K]: one product with two
 // accumulators and the activation in the epilogue.  Splits (at most 8) reduce inside a cluster.
+// Options of the epilogue (TcGlu): glu_bias float [2F] (null: none) is added to gate and up before the activation;
+// glu_kind 1 takes the tanh form of gelu in the place of silu; glu_gates float [T, F / glu_ff] (null: none) multiplies
+// every block of glu_ff features of a token by a factor of its own.
 extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, int T, int F, int K,
                                    long long ldx, long long ldw, long long ldc, int force_splits,
                                    const void* next_w, long long next_bytes,
-                                   const float* row_sumsq, int sumsq_parts, int norm_width, float norm_eps, void* stream) {
+                                   const float* row_sumsq, int sumsq_parts, int norm_width, float norm_eps,
+                                   const float* glu_bias, int glu_kind, const float* glu_gates, int glu_ff, void* stream) {
     if (T <= 0 || F <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm_swiglu: K=%d", K);
+    if (glu_kind != 0 && glu_kind != 1) RB_REFUSE("gemm_swiglu: activation %d", glu_kind);
+    if (glu_gates && (glu_ff <= 0 || F % glu_ff)) RB_REFUSE("gemm_swiglu: %d features in blocks of %d", F, glu_ff);
     if (force_splits < 0 || force_splits > 8) RB_REFUSE("gemm_swiglu: %d splits (0 = choose, at most a cluster of 8)", force_splits);
     TcExtra ex;
     if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
+    ex.glu = TcGlu{glu_bias, glu_gates, glu_kind, glu_gates ? glu_ff : 1, glu_gates ? F / glu_ff : 1, F};
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)Wgu & 15))
         RB_REFUSE("gemm_swiglu: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
     cudaStream_t s = (cudaStream_t)stream;

@@ -356,6 +356,31 @@ def molitar_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 327
             "layers": out}
 
 
+def zegorax_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
+                  kv_rank: int = 192, rot_dim: int = 64, window: int = 1024, experts: int = 8, top: int = 2, positions: int = 8192) -> Dict:
+    """A Zegorax config.json at layer sizes that resemble a real model's: the layers cycle differential attention (`heads`
+    heads of two maps of head_dim / 2 each over heads / 4 key heads, values of head_dim, a quarter of each map rotated with
+    stretched frequencies) -> latent attention (heads of head_dim + rot_dim, values of head_dim, a query bottleneck of 3/4
+    of the width, a latent of kv_rank, a window) -> the delta rule with a decay per head (heads of head_dim over heads / 4
+    key heads, four taps); feed-forwards alternate between dense (tanh-gelu, biases) and mixtures of `experts` experts of
+    ff / 4 of which `top` are chosen."""
+    kv = kv_heads or max(1, heads // 4)
+    half = head_dim // 2
+    attention = {"heads": heads, "kv_heads": kv, "dim": half, "vdim": head_dim, "scale": half ** -0.5, "diff": 0.3,
+                 "rot": {"base": 1e6, "dims": half // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": 3 * width // 4, "kv_rank": kv_rank,
+              "scale": (head_dim + rot_dim) ** -0.5, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": rot_dim}}
+    delta = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "conv": 4}
+    mixers = (("attention", attention), ("latent_attention", latent), ("delta", delta))
+    out = []
+    for i in range(layers):
+        kind, m = mixers[i % 3]
+        mlp = {"kind": "dense", "ff": ff} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": experts, "top": top}}
+        out.append({"type": kind, "mixer": m, "mlp": mlp})
+    return {"architecture": "Zegorax", "vocab": vocab, "width": width, "max_positions": positions, "norm": {"eps": 1e-5}, "layers": out}
+
+
 def qwen3_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
                 positions: int = 8192) -> Dict:
     """The closest existing design at the same layer sizes."""

@@ -935,12 +935,18 @@ def gemm_bf16_residual_norm(a: torch.Tensor, w: torch.Tensor, residual: torch.Te
     return rows, sumsq
 
 
-def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: int = 0, row_scale=None) -> bool:
+def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: int = 0, row_scale=None,
+                     act: str = "silu", bias: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None, ff: int = 0) -> bool:
     """out[T,F] (bf16) = silu(a Wg^T) * (a Wu^T), w_gate_up = [Wg; Wu] of shape [2F, K]: one tensor-core
     product with two accumulators and the activation in its epilogue.  Returns False (and does
-    nothing) if TMA cannot address the operands; the caller then runs the two-kernel form."""
+    nothing) if TMA cannot address the operands; the caller then runs the two-kernel form.
+    Options of the epilogue, as in glu_act: `act` ("silu" or "gelu_tanh"), `bias` (float32 [2F], added to gate and up
+    before the activation), `gates` (float32 [T, F // ff]: a factor per token and block of ff features)."""
     T, K = a.shape
     F_ = out.shape[1]
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == 2 * F_), "gemm_swiglu: the bias is float32 [2F]")
+    _need(gates is None or (ff > 0 and F_ % ff == 0 and gates.dtype == torch.float32 and gates.is_contiguous() and
+                            tuple(gates.shape) == (T, F_ // ff)), "gemm_swiglu: gates float32 [T, F / ff]")
     _need(w_gate_up.shape == (2 * F_, K) and out.shape[0] == T, "gemm_swiglu: shapes")
     _need(a.dtype == w_gate_up.dtype == out.dtype == torch.bfloat16, "gemm_swiglu: bfloat16 tensors")
     _need(a.stride(1) == 1 and w_gate_up.stride(1) == 1 and out.stride(1) == 1, "gemm_swiglu: rows contiguous")
@@ -949,7 +955,8 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     nw, nb = _next_range(w_gate_up) if T <= STREAMING_TOKENS else (c_void_p(0), c_longlong(0))
     _check(lib().rb_gemm_bf16_swiglu(_p(a), _p(w_gate_up), _p(out), c_int(T), c_int(F_), c_int(K),
                                      c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
-                                     c_int(splits), nw, nb, *_row_scale_args(row_scale, T), _stream()),
+                                     c_int(splits), nw, nb, *_row_scale_args(row_scale, T), _p(bias), c_int(GLU_ACTS[act]), _p(gates),
+                                     c_int(ff), _stream()),
            f"gemm+swiglu {2 * F_}x{K}", 4.0 * T * F_ * K, 2.0 * (T * K + 2 * F_ * K + T * F_))
     return True
 

@@ -55,8 +55,9 @@ class SwiGLU(FeedForward):
 
 class GatedFFN(FeedForward):
     """down( f(x Wg^T + bg) * (x Wu^T + bu) ) + bd with f = silu or the tanh form of gelu and optional biases on all three
-    projections (tensors `<name>.b`).  Gate and up are one product that leaves 32-bit sums; `ops.glu_act` adds the biases,
-    applies f and rounds once.  The last bias goes into the stream before the last product, so that the product may
+    projections (tensors `<name>.b`).  Gate and up are one product; in bfloat16 its epilogue adds the biases to the 32-bit
+    sums, applies f and rounds once (`ops.gemm_bf16_swiglu`), else the product leaves 32-bit sums and `ops.glu_act` does the
+    same.  The last bias goes into the stream before the last product, so that the product may
     still do the work of the norm that reads the stream next."""
 
     def __init__(self, hidden: int, intermediate: int, activation: str = "silu", bias: bool = False,
@@ -89,10 +90,11 @@ class GatedFFN(FeedForward):
 
     def forward(self, ctx, xn, residual):
         T = xn.shape[0]
-        gu = matmul(ctx, xn, self.w_gate_up, out_dtype=torch.float32)
         act = torch.empty((T, self.inter), dtype=xn.dtype, device=xn.device)
-        if T:
-            ops.glu_act(gu, act, self.activation, self.b_gate_up)
+        fused = T and xn.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and \
+            ops.gemm_bf16_swiglu(xn, self.w_gate_up, act, act=self.activation, bias=self.b_gate_up)
+        if T and not fused:
+            ops.glu_act(matmul(ctx, xn, self.w_gate_up, out_dtype=torch.float32), act, self.activation, self.b_gate_up)
         if self.b_down is None or T == 0:
             return matmul_into_residual(ctx, act, self.w_down, residual)
         if getattr(ctx, "fresh_residual", False):

@@ -73,7 +73,10 @@ class ExpertMixture(FeedForward):
         gates, ident = ops.moe_router(xn, self.w_router, self.correction, self.E, self.top, mode=self.route)     # 32-bit, product and choice
         if self.gated:
             act = torch.empty((T, self.E * self.ff), dtype=xn.dtype, device=xn.device)
-            if T:
+            # bfloat16: the activation and the expert's weight in the product's epilogue; else 32-bit sums and a kernel behind them
+            fused = T and xn.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and \
+                ops.gemm_bf16_swiglu(xn, self.w_up, act, act=self.activation, gates=gates, ff=self.ff)
+            if T and not fused:
                 ops.glu_act(matmul(ctx, xn, self.w_up, out_dtype=torch.float32), act, self.activation, None, gates, self.ff)
         else:
             act = ops.relu2_gate(matmul(ctx, xn, self.w_up), gates, self.ff)

@@ -122,6 +122,35 @@ def test_gated_activation_with_biases_and_expert_weights(act, dtype):
         _close(out.float(), want, 1e-5 if dtype == torch.float32 else 1e-2, f"{act} bias {with_bias} gates {with_gates}")
 
 
+@pytest.mark.parametrize("T", [1, 8, 40, 100, 300, 700])
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+def test_gated_pair_product_with_the_activation_in_its_epilogue(T, act):
+    """The tensor-core product of the gated pair at the token counts of its kernels (split over a cluster, streaming,
+    persistent) with biases, either activation and a weight per token and expert: against 64-bit sums of the same
+    bfloat16 operands."""
+    from reinfer_b200 import ops
+    g = torch.Generator().manual_seed(T)
+    K, E, ff = 192, 5, 72
+    F = E * ff
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    bias = torch.randn(2 * F, generator=g) * 0.5
+    gates = torch.rand(T, E, generator=g) * (torch.rand(T, E, generator=g) < 0.5)
+    f = plain.silu if act == "silu" else plain.gelu_tanh
+    z = x.double() @ w.double().t()
+    for with_bias, with_gates in ((True, False), (False, True), (True, True), (False, False)):
+        out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+        assert ops.gemm_bf16_swiglu(x.to(DEV), w.to(DEV), out, act=act, bias=bias.to(DEV) if with_bias else None,
+                                    gates=gates.to(DEV) if with_gates else None, ff=ff)
+        bb = bias.double() if with_bias else torch.zeros(2 * F, dtype=torch.float64)
+        want = f(z[:, :F] + bb[:F]) * (z[:, F:] + bb[F:])
+        if with_gates:
+            want = want * gates.double().repeat_interleave(ff, dim=1)
+        _close(out.float(), want, 1e-2, f"{act} bias {with_bias} gates {with_gates}")
+        if with_gates:
+            assert (out.float().cpu()[gates.repeat_interleave(ff, dim=1) == 0] == 0).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_per_head_maps_with_a_gate(dtype):
     from reinfer_b200 import ops
