@@ -366,7 +366,7 @@ def zegorax_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 327
     ff / 4 of which `top` are chosen."""
     kv = kv_heads or max(1, heads // 4)
     half = head_dim // 2
-    attention = {"heads": heads, "kv_heads": kv, "dim": half, "vdim": head_dim, "scale": half ** -0.5, "diff": 0.3,
+    attention = {"heads": heads, "kv_heads": kv, "dim": half, "vdim": head_dim, "scale": half ** -0.5, "diff": 0.2,
                  "rot": {"base": 1e6, "dims": half // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
     latent = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": 3 * width // 4, "kv_rank": kv_rank,
               "scale": (head_dim + rot_dim) ** -0.5, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": rot_dim}}

@@ -70,7 +70,7 @@ TINY_B = {"architecture": "Zegorax", "vocab": 97, "width": 52, "max_positions": 
 TINY_C = {"architecture": "Zegorax", "vocab": 130, "width": 96, "max_positions": 300, "norm": {"eps": 1e-6},
           "loop": {"start": 0, "stop": 1, "times": 3},
           "layers": [_layer(_lat(16, 16, 16, 8, 32, 48, 0.18, _rot(10000.0, 16), window=40), _moe(32, 16, 4)),
-                     _layer(_att(8, 2, 32, 16, 0.15, 0.3, _rot(10000.0, 32, (4.0, 1.0, 4.0, 64))), _dense(64)),
+                     _layer(_att(8, 2, 32, 16, 0.15, 0.45, _rot(10000.0, 32, (2.0, 1.0, 8.0, 64))), _dense(64)),
                      _layer(_delta(4, 4, 32, 16, 4), _moe(16, 8, 2)),
                      _layer(_att(4, 4, 16, 16, 0.3, 0.25, _rot(800.0, 8)), None),
                      _layer(_delta(8, 2, 16, 32, 2), _dense(48))]}
@@ -78,7 +78,7 @@ TINY_C = {"architecture": "Zegorax", "vocab": 130, "width": 96, "max_positions":
 #    products and the attention run on the tensor cores (not in TINY: its tests name it)
 TINY_D = {"architecture": "Zegorax", "vocab": 500, "width": 256, "max_positions": 512, "norm": {"eps": 1e-5},
           "loop": {"start": 1, "stop": 2, "times": 2},
-          "layers": [_layer(_att(4, 2, 64, 64, 0.12, 0.3, _rot(10000.0, 32, (4.0, 1.0, 4.0, 128))), _dense(512)),
+          "layers": [_layer(_att(4, 2, 64, 64, 0.12, 0.4, _rot(10000.0, 32, (8.0, 1.0, 4.0, 128))), _dense(512)),
                      _layer(_lat(4, 64, 32, 64, 128, 96, 0.1, _rot(10000.0, 32), window=100), _moe(128, 8, 2)),
                      _layer(_delta(4, 2, 64, 64, 4), _moe(64, 8, 2)),
                      _layer(_att(2, 1, 128, 128, 0.09, 0.2, _rot(500000.0, 128)), _dense(384))]}
