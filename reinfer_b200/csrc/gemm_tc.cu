@@ -594,6 +594,14 @@ struct TcRows {
     int sumsq_parts;
     float inv_width, eps;
     TcGlu glu;                           // the gated pair's epilogue (MODE 1)
+    // A grouped product (tile_group null: none): the token tiles are sorted by group - an expert of a mixture - so that
+    // token tile i holds rows of group tile_group[i] only, and only the first *live_tiles token tiles hold rows at all
+    // (both written on the device by the kernel that sorted the rows).  Group e's weights start w_row_step * e rows
+    // further down and w_k_step * e columns further right in W; up_offset is the distance from a gate row to its up row
+    // (MODE 1, where N counts one group's features).
+    const int* tile_group;
+    const int* live_tiles;
+    int w_row_step, w_k_step, up_offset;
 };
 
 template <int BN, int STAGES, int MODE, int ROWS = 2 * TC_BM>
@@ -624,6 +632,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     TcPersistShared* sh = (TcPersistShared*)(smem + (size_t)STAGES * STAGE_BYTES);
     const uint32_t smem_base = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (rs.live_tiles) {                                          // a grouped product: how many token tiles hold rows is known on the device only
+        pdl_wait();
+        const int live = *rs.live_tiles;
+        t_tiles = live < t_tiles ? live : t_tiles;
+    }
     const int total_tiles = t_tiles * n_tiles;
     const int nkb = (K + TC_BK - 1) / TC_BK;
     volatile int* abort_flag = &sh->abort_flag;
@@ -659,6 +672,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         [[maybe_unused]] int plocal = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++plocal) {
             const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * FEATS;
+            const int grp = rs.tile_group ? rs.tile_group[tile % t_tiles] : 0;
+            const int w_row = n0 + grp * rs.w_row_step, w_k = grp * rs.w_k_step;        // where this tile's weights start
+            const int up_row = (rs.tile_group ? rs.up_offset : N) + w_row;
             [[maybe_unused]] long long waited = 0;
             for (int kb = 0; kb < nkb; ++kb) {
 #ifdef RB_TIMELINE
@@ -673,8 +689,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 const uint32_t full = full0 + 8 * s;
                 mbar_expect_tx_lead(full, STAGE_BYTES, lead);
                 const uint32_t dst = smem_base + s * STAGE_BYTES;
-                tma_load_2d_lead(dst, &map_w, kb * TC_BK, n0, full, lead);      // MODE 2: the map's box has ROWS rows, MODE 1: ROWS / 2
-                if (DUAL) tma_load_2d_lead(dst + W1_BYTES, &map_w, kb * TC_BK, N + n0, full, lead);
+                tma_load_2d_lead(dst, &map_w, kb * TC_BK + w_k, w_row, full, lead);      // MODE 2: the map's box has ROWS rows, MODE 1: ROWS / 2
+                if (DUAL) tma_load_2d_lead(dst + W1_BYTES, &map_w, kb * TC_BK + w_k, up_row, full, lead);
                 tma_load_2d_lead(dst + W_BYTES, &map_x, kb * TC_BK, t0, full, lead);
                 ++issued;
                 if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -1707,6 +1723,39 @@ extern "C" int rb_gemm_bf16_swiglu(const void* X, const void* Wgu, void* act, in
         case 128: return launch_tc<128, 4, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
         default: return launch_tc<256, 3, true>(mw, mx, act, nullptr, 0, T, F, K, ldc, 0, force_splits, ex, s);
     }
+}
+
+// A grouped product over rows sorted by group (an expert of a mixture; see TcRows): X [R, K] bfloat16 holds the rows in
+// tiles of 128 that belong to one group each, tile_group [ceil(R / 128)] and live_tiles [1] are int32 on the device.
+//   dual != 0: act [R, N] bfloat16 = f(X Wg_e^T) * (X Wu_e^T) with W = [all groups' gate rows; all groups' up rows] of
+//              n_groups * N rows each (f: glu_kind as in rb_gemm_bf16_swiglu).
+//   dual == 0: C [R, N] float = X W_e^T with W [N, n_groups * K] holding the groups' matrices side by side.
+// Rows of tiles beyond *live_tiles are not touched.  K and N multiples of 8; the persistent kernels at every R.
+extern "C" int rb_gemm_bf16_grouped(const void* X, const void* W, void* C, int dual, int R, int N, int K, int n_groups,
+                                    long long ldx, long long ldw, long long ldc, const int* tile_group, const int* live_tiles,
+                                    int glu_kind, void* stream) {
+    if (R <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || N % 8 || n_groups <= 0) RB_REFUSE("gemm_grouped: K %d, N %d (multiples of 8), %d groups", K, N, n_groups);
+    if (!tile_group || !live_tiles) RB_REFUSE("gemm_grouped: the tiles' groups and their count are needed");
+    if (glu_kind != 0 && glu_kind != 1) RB_REFUSE("gemm_grouped: activation %d", glu_kind);
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        RB_REFUSE("gemm_grouped: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
+    TcExtra ex;
+    if (tc_extra(&ex, nullptr, 0, nullptr, 0, 0, 0.0f, R)) return -1;
+    ex.glu = TcGlu{nullptr, nullptr, glu_kind, 1, 1, N};
+    TcRows rs = tc_rows(ex);
+    rs.tile_group = tile_group; rs.live_tiles = live_tiles;
+    CUtensorMap mw, mx;
+    if (rb_tensor_map_bf16(X, R, K, ldx, 128, &mx)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dual) {
+        rs.w_row_step = N; rs.w_k_step = 0; rs.up_offset = n_groups * N;
+        if (rb_tensor_map_bf16(W, 2LL * n_groups * N, K, ldw, TC_BM, &mw)) return -1;
+        return launch_tc_persistent<128, 4, 1, 256>(mw, mx, C, R, N, K, ldc, 0, s, TcHeads{}, rs);
+    }
+    rs.w_row_step = 0; rs.w_k_step = K; rs.up_offset = 0;
+    if (rb_tensor_map_bf16(W, N, (long long)n_groups * K, ldw, 256, &mw)) return -1;
+    return launch_tc_persistent<128, 4, 2, 256>(mw, mx, C, R, N, K, ldc, 1, s, TcHeads{}, rs);
 }
 
 // What the decode product (T <= 16) would choose for N output features and K: out[0] = splits, out[1..8] = the

@@ -1192,6 +1192,47 @@ def rows_axpy(dst: torch.Tensor, a: torch.Tensor, src: torch.Tensor, store: bool
                               c_int(int(store)), _stream()), "rows_axpy")
 
 
+def moe_grouped_experts(x: torch.Tensor, gates: torch.Tensor, top: int, w_gate_up: torch.Tensor, w_down: torch.Tensor, ff: int,
+                        act: str, dst: torch.Tensor, store: bool = False) -> bool:
+    """dst[t] (+)= sum over the experts e that token t chose of gates[t, e] * W_down,e (f(W_gate,e x[t]) * (W_up,e x[t])), computing
+    only the chosen (token, expert) pairs: the tokens' rows are copied into an array sorted by expert (every expert's stretch
+    padded to whole tiles of 128 rows) and two grouped tensor-core products run over it (csrc/moe_group.cu, rb_gemm_bf16_grouped).
+    x [T, h] bfloat16; gates float32 [T, E], zero where an expert was not chosen, at most `top` non-zero a row; w_gate_up
+    [2 E ff, h] = [all experts' gate rows; all experts' up rows]; w_down [h, E ff], the experts side by side; dst float32
+    [T, h].  Nothing comes back to the host.  Returns False (and does nothing) where this form does not apply."""
+    T, h = x.shape
+    E = gates.shape[1]
+    if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16 or T == 0 or T > 65535:
+        return False
+    if h % 8 or ff % 8 or x.data_ptr() % 16 or w_gate_up.data_ptr() % 16 or w_down.data_ptr() % 16 or not (x.is_contiguous() and
+            w_gate_up.is_contiguous() and w_down.is_contiguous()):
+        return False
+    _need(tuple(w_gate_up.shape) == (2 * E * ff, h) and tuple(w_down.shape) == (h, E * ff) and gates.dtype == torch.float32 and
+          gates.is_contiguous() and dst.dtype == torch.float32 and dst.is_contiguous() and tuple(dst.shape) == (T, h), "moe_grouped_experts: shapes")
+    dev = x.device
+    tiles = -(-(T * top + E * 127) // 128)
+    ints = torch.empty(E + T * E + E + tiles + 1 + T * top, dtype=torch.int32, device=dev)
+    count, pos, seg, tile_group, live, rows = torch.split(ints, [E, T * E, E, tiles, 1, T * top])
+    w = torch.empty((T, top), dtype=torch.float32, device=dev)
+    xs = torch.empty((tiles * 128, h), dtype=torch.bfloat16, device=dev)
+    _check(lib().rb_moe_group_plan(_p(x), c_int(dt(x)), _p(gates), _p(count), _p(pos), _p(seg), _p(tile_group), _p(live), _p(rows), _p(w),
+                                   _p(xs), c_int(T), c_int(E), c_int(h), c_int(top), c_int(tiles), _stream()), "moe_group_plan",
+           0.0, float((1 + top) * T * h * 2))
+    global launches
+    launches += 2
+    inner = torch.empty((tiles * 128, ff), dtype=torch.bfloat16, device=dev)
+    _check(lib().rb_gemm_bf16_grouped(_p(xs), _p(w_gate_up), _p(inner), c_int(1), c_int(tiles * 128), c_int(ff), c_int(h), c_int(E),
+                                      c_longlong(h), c_longlong(h), c_longlong(ff), _p(tile_group), _p(live), c_int(GLU_ACTS[act]), _stream()),
+           f"gemm+swiglu grouped {2 * ff}x{h}", 4.0 * T * top * ff * h, 2.0 * (T * top * (h + ff) + 2 * E * ff * h))
+    y = torch.empty((tiles * 128, h), dtype=torch.float32, device=dev)
+    _check(lib().rb_gemm_bf16_grouped(_p(inner), _p(w_down), _p(y), c_int(0), c_int(tiles * 128), c_int(h), c_int(ff), c_int(E),
+                                      c_longlong(ff), c_longlong(E * ff), c_longlong(h), _p(tile_group), _p(live), c_int(0), _stream()),
+           f"gemm grouped {h}x{ff}", 2.0 * T * top * ff * h, 2.0 * (T * top * ff + E * ff * h) + 4.0 * T * top * h)
+    _check(lib().rb_moe_group_combine(_p(dst), _p(y), _p(rows), _p(w), c_int(T), c_int(h), c_int(top), c_int(int(store)), _stream()),
+           "moe_group_combine", 0.0, float(T * h * 4 * (top + 2)))
+    return True
+
+
 GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
 
 

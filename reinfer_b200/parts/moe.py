@@ -12,6 +12,12 @@ Two options make the other common form.  `gated=True`: an expert is down(f(gate(
 (`correction_name`) is a bias of the logits, the `top` largest logits are chosen and the weights are the softmax over the
 chosen logits alone.
 
+Over many tokens (a prompt portion) the stacked products compute every expert for every token where a token uses `top`
+of them.  A gated mixture in bfloat16 whose tokens use at most half of the experts then takes the grouped form
+(`ops.moe_grouped_experts`): rows sorted by expert on the device, two grouped tensor-core products over the chosen
+pairs alone, the weighted sum per token in the order of the experts.  A decode step's few tokens touch most experts
+anyway and keep the stacked form.
+
 The experts' up matrices are stacked by rows at load and their down matrices side by side, and the router's choice
 is kept dense (gates [T, experts], zero where an expert was not chosen): one product makes every expert's inner
 activations, the activation kernel multiplies each by its token's gate, and one product with the stacked down
@@ -20,12 +26,18 @@ token's result never depends on what else is in the batch.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
 from ..weights.params import ParamSpec
 from .base import FeedForward, register_part
 from .linear import matmul, matmul_into_residual
+
+
+GROUPED = os.environ.get("REINFER_B200_MOE_GROUPED", "1") != "0"    # 0: the stacked products at every token count
+GROUPED_FROM = 256                                                  # tokens of a step from which the grouped form is taken
 
 
 class ExpertMixture(FeedForward):
@@ -71,6 +83,12 @@ class ExpertMixture(FeedForward):
     def forward(self, ctx, xn, residual):
         T = xn.shape[0]
         gates, ident = ops.moe_router(xn, self.w_router, self.correction, self.E, self.top, mode=self.route)     # 32-bit, product and choice
+        if self.gated and ident is None and T >= GROUPED_FROM and 2 * self.top <= self.E and GROUPED and \
+                getattr(ctx, "norm_ahead", None) is None:
+            fresh = bool(getattr(ctx, "fresh_residual", False))
+            if ops.moe_grouped_experts(xn, gates, self.top, self.w_up, self.w_down, self.ff, self.activation, residual, store=fresh):
+                ctx.fresh_residual = False
+                return None
         if self.gated:
             act = torch.empty((T, self.E * self.ff), dtype=xn.dtype, device=xn.device)
             # bfloat16: the activation and the expert's weight in the product's epilogue; else 32-bit sums and a kernel behind them

@@ -151,6 +151,38 @@ def test_gated_pair_product_with_the_activation_in_its_epilogue(T, act):
             assert (out.float().cpu()[gates.repeat_interleave(ff, dim=1) == 0] == 0).all()
 
 
+@pytest.mark.parametrize("T,E,top,h,ff", [(300, 8, 2, 64, 72), (257, 4, 1, 128, 128), (1000, 16, 4, 192, 200), (130, 6, 3, 64, 8)])
+def test_experts_over_rows_sorted_by_expert(T, E, top, h, ff):
+    """The grouped form of a gated mixture (only the chosen pairs are computed) against 64-bit sums over the same bfloat16
+    operands, with inner widths that are no multiple of a tile (a tile of weight rows then reaches into the next
+    expert's) and with experts that nobody chose."""
+    from reinfer_b200 import ops
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, h, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(E, ff, h, generator=g) * h ** -0.5).to(torch.bfloat16)
+    wu = (torch.randn(E, ff, h, generator=g) * h ** -0.5).to(torch.bfloat16)
+    wd = (torch.randn(E, h, ff, generator=g) * ff ** -0.5).to(torch.bfloat16)
+    z = torch.randn(T, E, generator=g)
+    z[:, 1] = -50.0                                                # an expert that nobody chooses
+    val, idx = torch.topk(z, top, dim=-1)
+    gates = torch.zeros(T, E).scatter_(1, idx, torch.softmax(val, -1))
+    want = torch.zeros(T, h, dtype=torch.float64)
+    for e in range(E):
+        rows = (gates[:, e] > 0).nonzero().flatten()
+        if len(rows):
+            xe = x[rows].double()
+            inner = (plain.silu(xe @ wg[e].double().t()) * (xe @ wu[e].double().t())).to(torch.bfloat16).double()
+            want[rows] += gates[rows, e:e + 1].double() * (inner @ wd[e].double().t())
+    base = torch.randn(T, h, generator=g)
+    w_gu = torch.cat([wg.reshape(E * ff, h), wu.reshape(E * ff, h)]).contiguous().to(DEV)
+    w_down = wd.permute(1, 0, 2).reshape(h, E * ff).contiguous().to(DEV)
+    for store in (False, True):
+        dst = base.clone().to(DEV)
+        assert ops.moe_grouped_experts(x.to(DEV), gates.to(DEV), top, w_gu, w_down, ff, "silu", dst, store=store)
+        _close(dst, want if store else want + base.double(), 5e-3, f"store {store}")
+    assert ops.status_word() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_per_head_maps_with_a_gate(dtype):
     from reinfer_b200 import ops
