@@ -85,7 +85,8 @@ struct TcGlu {
 
 __device__ __forceinline__ float tc_glu(const TcGlu& gl, float g, float u, int feat, int tok) {
     if (gl.bias) { g += gl.bias[feat]; u += gl.bias[gl.F + feat]; }
-    const float a = gl.kind == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+    // tanh-gelu: 0.5 (1 + tanh(u)) = 1 / (1 + exp(-2u)), u = sqrt(2/pi) (g + 0.044715 g^3) - one exponential, as silu
+    const float a = g / (1.0f + expf(gl.kind == 1 ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g));
     float v = a * u;
     if (gl.gates) v *= gl.gates[(size_t)tok * gl.n_exp + feat / gl.ff];
     return v;

@@ -10,11 +10,8 @@
 #include "common.cuh"
 
 __device__ __forceinline__ float glu_f(float z, int kind) {
-    if (kind == 1) {
-        const float c = 0.7978845608028654f;                  // sqrt(2 / pi)
-        return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
-    }
-    return z / (1.0f + expf(-z));
+    // tanh-gelu: 0.5 (1 + tanh(u)) = 1 / (1 + exp(-2u)) with u = sqrt(2/pi) (z + 0.044715 z^3): one exponential, as silu
+    return z / (1.0f + expf(kind == 1 ? -1.5957691216057308f * (z + 0.044715f * z * z * z) : -z));
 }
 
 template <typename TI, typename TO>

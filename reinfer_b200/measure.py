@@ -358,16 +358,16 @@ def molitar_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 327
 
 def zegorax_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
                   kv_rank: int = 192, rot_dim: int = 64, window: int = 1024, experts: int = 8, top: int = 2, positions: int = 8192) -> Dict:
-    """A Zegorax config.json at layer sizes that resemble a real model's: the layers cycle differential attention (`heads`
-    heads of two maps of head_dim / 2 each over heads / 4 key heads, values of head_dim, a quarter of each map rotated with
-    stretched frequencies) -> latent attention (heads of head_dim + rot_dim, values of head_dim, a query bottleneck of 3/4
-    of the width, a latent of kv_rank, a window) -> the delta rule with a decay per head (heads of head_dim over heads / 4
-    key heads, four taps); feed-forwards alternate between dense (tanh-gelu, biases) and mixtures of `experts` experts of
-    ff / 4 of which `top` are chosen."""
+    """A Zegorax config.json at layer sizes that resemble a real model's: the layers cycle differential attention (heads / 2
+    heads of two maps of head_dim each over an eighth as many key heads, values of head_dim - the query and key projections
+    are as large as those of `heads` plain heads - a quarter of each map rotated with stretched frequencies) -> latent
+    attention (heads of head_dim + rot_dim, values of head_dim, a query bottleneck of 3/4 of the width, a latent of kv_rank,
+    a window) -> the delta rule with a decay per head (heads of head_dim over heads / 4 key heads, four taps); feed-forwards
+    alternate between dense (tanh-gelu, biases) and mixtures of `experts` experts of ff / 4 of which `top` are chosen."""
     kv = kv_heads or max(1, heads // 4)
-    half = head_dim // 2
-    attention = {"heads": heads, "kv_heads": kv, "dim": half, "vdim": head_dim, "scale": half ** -0.5, "diff": 0.2,
-                 "rot": {"base": 1e6, "dims": half // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    pairs = max(1, heads // 2)
+    attention = {"heads": pairs, "kv_heads": max(1, pairs // 4), "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "diff": 0.2,
+                 "rot": {"base": 1e6, "dims": head_dim // 4, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
     latent = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": 3 * width // 4, "kv_rank": kv_rank,
               "scale": (head_dim + rot_dim) ** -0.5, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": rot_dim}}
     delta = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "conv": 4}

@@ -83,8 +83,8 @@ class ExpertMixture(FeedForward):
     def forward(self, ctx, xn, residual):
         T = xn.shape[0]
         gates, ident = ops.moe_router(xn, self.w_router, self.correction, self.E, self.top, mode=self.route)     # 32-bit, product and choice
-        if self.gated and ident is None and T >= GROUPED_FROM and 2 * self.top <= self.E and GROUPED and \
-                getattr(ctx, "norm_ahead", None) is None:
+        if self.gated and ident is None and T >= GROUPED_FROM and 2 * self.top <= self.E and GROUPED:
+            # (a step of this many tokens is beyond the products that do the next norm's work: nothing is lost by not asking)
             fresh = bool(getattr(ctx, "fresh_residual", False))
             if ops.moe_grouped_experts(xn, gates, self.top, self.w_up, self.w_down, self.ff, self.activation, residual, store=fresh):
                 ctx.fresh_residual = False
