@@ -445,6 +445,11 @@ def time_design(raw: Dict, prompt: int = 2048, batch: int = 8, context: int = 20
         try:
             for kind, entries in (("decode", [StepEntry(("d", b), [9 + b], [0]) for b in range(batch)]),
                                   ("prefill", [StepEntry("s", toks(prompt), [prompt - 1])])):
+                if kind == "prefill":
+                    # once unmeasured: the decode steps before split the allocator's large blocks, and a prompt's first
+                    # step after them waits for new ones - time that the events would put on whatever kernel comes next
+                    engine.step([StepEntry("w", toks(prompt), [prompt - 1])])
+                    engine.finish("w")
                 prof = ops.SegmentProfiler()
                 torch.cuda.synchronize()
                 torch.cuda._sleep(40_000_000)
