@@ -568,6 +568,7 @@ struct TcPersistShared {
     uint32_t tmem_base;
     int abort_flag;
     __align__(16) float head_w[2][128];      // MODE 3: the q and k norm weights
+    __align__(16) float glu_bias[2][2 * TC_BM];   // MODE 1: the gate and up biases of a tile's features, per accumulator
 };
 
 // MODE 3 of the persistent kernel: the product is the attention's q/k/v projection with heads of 128, and a tile's 256
@@ -772,6 +773,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const int a = local & 1;
             const int t0 = (tile % t_tiles) * BN, n0 = (tile / t_tiles) * FEATS;
+            if (DUAL && rs.glu.bias) {
+                // the tile's biases come into shared memory while its products still run (read from global memory in
+                // the loop below they cost a trip to L2 per 16 features that nothing hides: 35 us of a 150 us product)
+                const int i = threadIdx.x - 64, f = n0 + i;
+                sh->glu_bias[a][i] = f < N ? rs.glu.bias[f] : 0.0f;
+                sh->glu_bias[a][TC_BM + i] = f < N ? rs.glu.bias[rs.glu.F + f] : 0.0f;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             if (!mbar_wait(smem_u32(&sh->acc_full[a]), (uint32_t)(local >> 1) & 1, abort_flag, 14)) break;
 #ifdef RB_TIMELINE
             if (warp == 2 && lane == 0) TT(local, 4, tl_now());
@@ -789,6 +798,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 // a lane is a token; columns 0..FEATS-1 hold its gate features, the next FEATS the up features of the same tile
                 const int tok = t0 + q * 32 + lane;
                 bf16* row = (bf16*)C + (size_t)tok * ldc + n0;
+                TcGlu gl = rs.glu;
+                const bool biased = gl.bias != nullptr;
+                gl.bias = nullptr;                                 // added here, from shared memory
+                const float* sb = sh->glu_bias[a];
 #pragma unroll 1
                 for (int c0 = 0; c0 < FEATS; c0 += 16) {
                     if (n0 + c0 >= N) break;
@@ -800,10 +813,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                         uint32_t o[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const float g0 = __uint_as_float(r[2 * j]) * rf, u0 = __uint_as_float(r2[2 * j]) * rf;
-                            const float g1 = __uint_as_float(r[2 * j + 1]) * rf, u1 = __uint_as_float(r2[2 * j + 1]) * rf;
+                            float g0 = __uint_as_float(r[2 * j]) * rf, u0 = __uint_as_float(r2[2 * j]) * rf;
+                            float g1 = __uint_as_float(r[2 * j + 1]) * rf, u1 = __uint_as_float(r2[2 * j + 1]) * rf;
+                            if (biased) {
+                                g0 += sb[c0 + 2 * j]; u0 += sb[TC_BM + c0 + 2 * j];
+                                g1 += sb[c0 + 2 * j + 1]; u1 += sb[TC_BM + c0 + 2 * j + 1];
+                            }
                             const int f0 = min(n0 + c0 + 2 * j, N - 1), f1 = min(n0 + c0 + 2 * j + 1, N - 1);
-                            const __nv_bfloat162 v = __floats2bfloat162_rn(tc_glu(rs.glu, g0, u0, f0, tok), tc_glu(rs.glu, g1, u1, f1, tok));
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(tc_glu(gl, g0, u0, f0, tok), tc_glu(gl, g1, u1, f1, tok));
                             o[j] = *(const uint32_t*)&v;
                         }
                         if (vec_ok && n0 + c0 + 16 <= N) {
