@@ -378,6 +378,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int et = threadIdx.x - 64;                       // 0..127
             const int f4 = (et & 31) * 4, tsub = et >> 5;
             const int feat = n0 + f4;
+            // the gated pair's biases of this thread's four features: fetched once, before any token's sums
+            TcGlu gl = ex.glu;
+            float gate_b[4] = {0.f, 0.f, 0.f, 0.f}, up_b[4] = {0.f, 0.f, 0.f, 0.f};
+            if (DUAL && gl.bias) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int fi = min(feat + i, N - 1);
+                    gate_b[i] = gl.bias[fi]; up_b[i] = gl.bias[gl.F + fi];
+                }
+            }
+            gl.bias = nullptr;
             if (!DUAL && feat + 3 < N && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0 && out_mode != 0) {
                 // float results, four whole features: two tokens a trip (their partial sums from every rank and, for
                 // an accumulating product, the residual's old values are all on their way before the first is used)
@@ -529,7 +540,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (DUAL) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = tc_glu(ex.glu, v[i], u[i] * f, min(feat + i, N - 1), t0 + cb);
+                    for (int i = 0; i < 4; ++i) v[i] = tc_glu(gl, v[i] + gate_b[i], u[i] * f + up_b[i], min(feat + i, N - 1), t0 + cb);
                 }
                 const size_t at = (size_t)(t0 + cb) * ldc + feat;
 #pragma unroll

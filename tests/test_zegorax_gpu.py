@@ -174,6 +174,15 @@ def test_a_small_real_shape_on_the_tensor_core_paths(tmp_path, dtype):
         assert {"latent_prep", "rotary_heads_append", "diff_heads", "moe_router", "shortconv"} <= names, names
         assert any(n.startswith("fa_prefill") for n in names) and any(n.startswith("fa_decode") for n in names), names
         assert any(n.startswith("recurrence") for n in names) and "paged_attention_ref" not in names, names
+        # a portion of 256 tokens or more: the mixtures compute the chosen pairs only
+        prof = ops.SegmentProfiler()
+        old = ops.set_profiler(prof)
+        try:
+            prof.begin()
+            engine.step([StepEntry("g", seqs["r0"][:290], [289])])
+        finally:
+            ops.set_profiler(old)
+        assert any(n.startswith("gemm+swiglu grouped") for n in prof.summary()) and "moe_group_combine" in prof.summary(), set(prof.summary())
     else:
         assert "paged_attention_ref" in names and any(n.startswith("gemm_fma") for n in names), names
 
